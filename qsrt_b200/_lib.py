@@ -1,0 +1,59 @@
+"""ctypes binding of ``libqsrt_b200.so`` (the C ABI declared in ``include/qsrt_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+from pathlib import Path
+
+LIBRARY = Path(__file__).resolve().parent / "libqsrt_b200.so"
+
+OK = 0
+EINVAL, ESCRATCH, ECUDA, ENOTPD = -1, -2, -3, -4
+
+_c = ctypes
+_PTR = _c.c_void_p
+_SIGNATURES = {
+    "qsrtb_abi_version": (_c.c_int, []),
+    "qsrtb_last_error": (_c.c_char_p, []),
+    "qsrtb_lut_prepare": (_c.c_int, [_PTR, _c.c_int, _PTR, _PTR, _PTR]),
+    "qsrtb_viterbi_scratch_bytes": (_c.c_int, [_c.c_int, _c.c_int64, _c.POINTER(_c.c_size_t)]),
+    "qsrtb_quantize_tiles": (
+        _c.c_int,
+        [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_size_t, _PTR],
+    ),
+    "qsrtb_pack_trellis": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR]),
+    "qsrtb_unpack_decode": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR, _PTR, _PTR]),
+}
+
+
+def exported_symbols() -> tuple[str, ...]:
+    return tuple(_SIGNATURES)
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    if not LIBRARY.exists():
+        raise RuntimeError(
+            f"{LIBRARY} is missing: build it with `python -m qsrt_b200.build` "
+            "(there is no CPU or PyTorch fallback for the encoder kernels)"
+        )
+    handle = ctypes.CDLL(str(LIBRARY))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return handle
+
+
+def check(status: int, what: str) -> None:
+    if status == OK:
+        return
+    message = lib().qsrtb_last_error().decode("utf-8", "replace")
+    text = f"{what} failed (status {status}): {message}"
+    if status == EINVAL:
+        raise ValueError(text)
+    raise RuntimeError(text)

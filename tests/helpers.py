@@ -1,0 +1,85 @@
+"""Shared test inputs and the loader of the prebuilt reference extension."""
+
+from __future__ import annotations
+
+import importlib.util
+import sys
+from functools import lru_cache
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REF_EXT = ROOT / "oracle" / "_ref" / "qsrt_ref_sqg_ext.so"
+FAMILIES = ("normal", "scaled", "heavy", "spike")
+
+
+def make_tiles(family: str, tiles: int, seed: int) -> torch.Tensor:
+    """Seeded tile families with the distributions of the reference's kernel A/B harness
+    (scripts/benchmark_sqg_tile_encoder.py:98-116): unit normal; normal times a cycling scale
+    in {1/4 .. 4}; Student-t(3); normal with 1 % of entries multiplied by 100."""
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn((tiles, 256), generator=g, dtype=torch.float32)
+    if family == "normal":
+        return x
+    if family == "scaled":
+        cycle = torch.tensor([0.25, 0.5, 1.0, 2.0, 4.0])
+        return x * cycle[torch.arange(tiles) % 5][:, None]
+    if family == "heavy":
+        chi2 = torch.randn((tiles, 256, 3), generator=g).square().sum(-1)
+        return x * torch.rsqrt(chi2 / 3.0).clamp(max=1e3)
+    if family == "spike":
+        hit = torch.rand((tiles, 256), generator=g) < 0.01
+        return torch.where(hit, x * 100.0, x)
+    raise ValueError(family)
+
+
+def mixed_tiles(per_family: int, seed: int) -> torch.Tensor:
+    """All four families plus the reference's structural rows (tests/test_sqg_quantizer.py:
+    176-179: a row x100, a zero row, a row x-40) and two saturated rows of 1000.0."""
+
+    parts = [make_tiles(f, per_family, seed + i) for i, f in enumerate(FAMILIES)]
+    extra = make_tiles("normal", 5, seed + 99)
+    extra[0] *= 100.0
+    extra[1] = 0.0
+    extra[2] *= -40.0
+    extra[3] = 1000.0
+    extra[4] = -1000.0
+    return torch.cat(parts + [extra]).contiguous()
+
+
+@lru_cache(maxsize=1)
+def reference_extension():
+    """The UNMODIFIED reference CUDA extension built by oracle/build_ref.py, or None."""
+
+    if not REF_EXT.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("qsrt_ref_sqg_ext", REF_EXT)
+    module = importlib.util.module_from_spec(spec)
+    sys.modules["qsrt_ref_sqg_ext"] = module
+    spec.loader.exec_module(module)
+    return module
+
+
+def reference_quantize_tiles(tiles: torch.Tensor, lut_state: torch.Tensor, bits: int, context: int):
+    """Drive the reference kernel exactly as qsrt/sqg_quantizer.py:607-651 does."""
+
+    ext = reference_extension()
+    device = tiles.device
+    edges = 65536 >> bits
+    decisions = edges // 4 if bits == 2 else edges // 2 if bits <= 4 else edges
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    max_batch = max(256, 3 * sms)
+    costs = torch.zeros((max_batch, 2, edges), dtype=torch.float16, device=device)
+    trace = torch.empty((max_batch, 256, decisions), dtype=torch.uint8, device=device)
+    lut = lut_state.to(device=device, dtype=torch.uint8).contiguous()
+    abs_max = float(lut.view(torch.float8_e4m3fn).float().abs().amax())
+    if bits in (2, 3, 4):
+        lut = lut.reshape(1 << bits, edges // 2, 2).permute(1, 0, 2).contiguous().reshape(-1)
+    out = torch.empty_like(tiles)
+    idx = torch.empty_like(tiles, dtype=torch.int16)
+    ext.quantize_tiles_sqg(tiles.contiguous(), out, idx, costs, trace, lut, bits, context, abs_max)
+    torch.cuda.synchronize(device)
+    return out, idx
