@@ -65,6 +65,70 @@ int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-cor
                          void* scratch, size_t scratch_bytes,
                          void* stream);
 
+/* ---- H1: calibration Hessian accumulation ------------------------------------------------
+ * Replaces the chunked `accumulator.addmm_(x.T, x * w)` of weighted_covariance
+ * (qsrt/candidate_hessian.py:70-112) and _accumulate_hessian (qsrt/capture.py:714-731).
+ *   qsrtb_hessian_accumulate : lower triangle of  lower (+)= sum_r w[r] * rows[r]^T rows[r]
+ *                              (weights may be NULL = 1; accumulate 0 overwrites, 1 adds).
+ *   qsrtb_hessian_finish     : divides the lower triangle by weight_sum and mirrors it, giving
+ *                              the symmetric float32 covariance ((C + C^T) / 2 of the reference).
+ */
+int qsrtb_hessian_accumulate(const float* rows, const float* weights, int64_t n_rows, int d,
+                             int ld_rows, float* lower, int ld_h, int accumulate, void* stream);
+int qsrtb_hessian_finish(float* h, int d, int ld_h, double weight_sum, void* stream);
+
+/* ---- R1 / H2 / D1: blockwise 128-point Hadamard with a fused sign/scale vector ----------
+ * Replaces blockwise_preapply_had_l_/r_ and preapply_had_l/r together with the vector
+ * scaling next to them (qsrt/exl3_encoder_backend.py:275-320, 2654-2675, 2142-2145,
+ * 3031-3034; decode side qsrt/exl3_reference.py:230-243, 298-301).  In place on `batch`
+ * row-major matrices [rows, cols] (row pitch ld, matrix pitch x_stride).
+ *   axis 1: every 128-column block of every row  := block @ Had128 / sqrt(128)  ("had_r")
+ *   axis 0: every 128-row block of every column  := Had128 / sqrt(128) @ block  ("had_l")
+ *   scale (optional, one vector per matrix, pitch scale_stride): indexed by column when
+ *   scale_per_col else by row; divides when scale_divide else multiplies; applied to the
+ *   transformed values when scale_after else to the inputs.
+ *   row_sumsq (axis 1 only, optional): per-row sum of squares of the result, fixed order.
+ */
+int qsrtb_hadamard128(float* x, int batch, int rows, int cols, int ld, int64_t x_stride, int axis,
+                      const float* scale, int64_t scale_stride, int scale_per_col,
+                      int scale_divide, int scale_after, float* row_sumsq, int64_t sumsq_stride,
+                      void* stream);
+
+/* Column sums of squares of `batch` matrices (the out-channel RMS of regularize,
+ * qsrt/exl3_encoder_backend.py:2508-2521, 2634).  workspace: batch*ceil(rows/256)*cols floats. */
+int qsrtb_col_sumsq(const float* x, int batch, int rows, int cols, int ld, int64_t x_stride,
+                    float* out, int64_t out_stride, float* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* ---- H2: Cholesky factor -> unit block-lower LDL feedback factor, in place ---------------
+ * Replaces the tail of block_ldl and the diagonal clearing after it
+ * (qsrt/exl3_encoder_backend.py:372-393, 2152-2153): each 16-column block is multiplied by
+ * the inverse of its diagonal block; diagonal blocks and everything above them become 0.
+ */
+int qsrtb_block_ldl_normalize(float* chol, int n, int ld, void* stream);
+
+/* ---- L1: one 16-row step of the BlockLDLQ loop ----------------------------------------
+ * Replaces, for one 16-row block of `batch` stacked row-major matrices, the per-step chain of
+ * ldlq / ldlq_batched (qsrt/exl3_encoder_backend.py:502-520, 2040-2062): feedback add
+ * (`_apply_ldlq_feedback`, :408-417), reshape to 16x16 tiles, tensor-core permutation (:35-57),
+ * tile search, inverse permutation and scatter of the reconstruction.
+ *   w, wq, err : pointers to the FIRST of the 16 rows in matrix 0 (row pitch `ld`, matrix
+ *                pitch `w_stride`); err (= w - wq) may be NULL.
+ *   comp       : compensation rows [16, n] per matrix (pitch comp_ld / comp_stride) or NULL.
+ *   out_states : [n/16, 256] states per matrix for this row of tiles (pitch state_stride).
+ *   tile_map   : optional device list of the column tiles to encode (tile_map_count of
+ *                them, others untouched): one launch per rate of a mixed-rate column map
+ *                (ldlq_mixed, qsrt/exl3_encoder_backend.py:898-1082); NULL = all n/16 tiles.
+ * Encoder input is w (multiplier 0), w + comp (1) or w + multiplier * comp.
+ */
+int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier, int batch,
+                             int n, int ld, int comp_ld, int64_t w_stride, int64_t comp_stride,
+                             const uint8_t* lut_state, const uint8_t* lut_pm, int bits,
+                             int tailbite_context, int variant, float* wq, float* err,
+                             int16_t* out_states, int64_t state_stride, const int32_t* tile_map,
+                             int tile_map_count, void* scratch, size_t scratch_bytes,
+                             void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).
@@ -81,6 +145,13 @@ int qsrtb_pack_trellis(const int16_t* states, int64_t n_tiles, int bits, int16_t
 int qsrtb_unpack_decode(const int16_t* packed, int64_t n_tiles, int bits,
                         const uint8_t* lut_state, int16_t* out_states, uint8_t* out_e4m3,
                         void* stream);
+
+/* States [tiles_k, tiles_n, 256] (tensor-core element order) -> decoded row-major float32
+ * [tiles_k*16, tiles_n*16] in the regularised basis: LUT decode, inverse tile permutation and
+ * tile placement of decode_regularized_weight (qsrt/exl3_reference.py:108-140) in one pass.
+ */
+int qsrtb_states_to_matrix(const int16_t* states, int tiles_k, int tiles_n,
+                           const uint8_t* lut_state, float* out, int ld, void* stream);
 
 #ifdef __cplusplus
 }

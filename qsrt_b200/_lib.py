@@ -25,7 +25,29 @@ _SIGNATURES = {
         _c.c_int,
         [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_size_t, _PTR],
     ),
+    "qsrtb_ldlq_quantize_rows": (
+        _c.c_int,
+        [_PTR, _PTR, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,
+         _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_int64, _PTR, _c.c_int,
+         _PTR, _c.c_size_t, _PTR],
+    ),
+    "qsrtb_hessian_accumulate": (
+        _c.c_int, [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR]
+    ),
+    "qsrtb_hessian_finish": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _c.c_double, _PTR]),
+    "qsrtb_hadamard128": (
+        _c.c_int,
+        [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _c.c_int, _PTR, _c.c_int64,
+         _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int64, _PTR],
+    ),
+    "qsrtb_col_sumsq": (
+        _c.c_int,
+        [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _PTR, _c.c_int64, _PTR,
+         _c.c_size_t, _PTR],
+    ),
+    "qsrtb_block_ldl_normalize": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _PTR]),
     "qsrtb_pack_trellis": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR]),
+    "qsrtb_states_to_matrix": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _PTR, _PTR, _c.c_int, _PTR]),
     "qsrtb_unpack_decode": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR, _PTR, _PTR]),
 }
 

@@ -79,6 +79,34 @@ unpack_decode_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int b
     }
 }
 
+// states [kt, nt, 256] (tensor-core order) -> row-major float32 [kt*16, nt*16].
+// One block per tile; thread = row-major element, so the stores of a tile are 16 runs of 64 B.
+__global__ void __launch_bounds__(256)
+states_to_matrix_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, int tiles_n,
+                        const uint8_t* __restrict__ lut_state, float* __restrict__ out, int ld)
+{
+    __shared__ uint16_t sh[256];
+    const int e = threadIdx.x;  // row-major element: row = e / 16, col = e % 16
+    const int row = e >> 4, col = e & 15;
+    // position of (row, col) in tensor-core order (inverse of exl3_encoder_backend.py:35-57)
+    const int lane = ((col & 7) << 2) | ((row & 7) >> 1);
+    const int j = (row & 1) | ((row & 8) ? 2 : 0) | ((col & 8) ? 4 : 0);
+    const int src = lane * 8 + j;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        sh[e] = states[tile * 256 + e];
+        __syncthreads();
+        const uint8_t b = lut_state[sh[src]];
+        const int64_t tk = tile / tiles_n;
+        const int tn = int(tile - tk * tiles_n);
+        // E4M3 -> float: exact, via the bit pattern
+        const int ex = (b >> 3) & 15, m = b & 7;
+        float v = ex == 0 ? float(m) * 0.001953125f : __int_as_float(((ex + 120) << 23) | (m << 20));
+        if (b & 0x80) v = -v;
+        out[(tk * 16 + row) * int64_t(ld) + tn * 16 + col] = v;
+        __syncthreads();
+    }
+}
+
 int grid_for(int64_t blocks_wanted)
 {
     int device = 0, sms = 148;
@@ -119,5 +147,19 @@ extern "C" int qsrtb_unpack_decode(const int16_t* packed, int64_t n_tiles, int b
         reinterpret_cast<uint16_t*>(out_states), out_e4m3);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "unpack launch");
+    return QSRTB_OK;
+}
+
+extern "C" int qsrtb_states_to_matrix(const int16_t* states, int tiles_k, int tiles_n,
+                                      const uint8_t* lut_state, float* out, int ld, void* stream)
+{
+    if (tiles_k < 0 || tiles_n < 0 || ld < tiles_n * 16) return qsrtb_fail(QSRTB_EINVAL, "bad tile grid");
+    const int64_t n_tiles = int64_t(tiles_k) * tiles_n;
+    if (n_tiles == 0) return QSRTB_OK;
+    if (!states || !lut_state || !out) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
+    states_to_matrix_kernel<<<grid_for(n_tiles), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint16_t*>(states), n_tiles, tiles_n, lut_state, out, ld);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return qsrtb_fail_cuda(err, "states_to_matrix launch");
     return QSRTB_OK;
 }

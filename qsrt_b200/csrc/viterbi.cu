@@ -416,10 +416,45 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
     return valid;
 }
 
+// Where a CTA finds tile `t` and where its results go.
+//   rows_mode == 0: tiles are contiguous [n, 256] in tensor-core element order.
+//   rows_mode == 1: tile t is the 16x16 block (matrix b = t / tiles_n, column tile t % tiles_n)
+//     of a 16-row slab of row-major matrices; the encoder input is w + multiplier * comp
+//     (exl3_encoder_backend.py:408-417, 502-509) and the reconstruction goes back to the
+//     same 16 rows of wq (and, optionally, w - wq to err), so the per-step gather, permute,
+//     un-permute and scatter kernels of the reference's LDLQ loop disappear.
+struct TileIO {
+    const float* tiles;
+    float* out_tiles;
+    uint16_t* out_states;
+    const float* w;
+    const float* comp;
+    float* wq;
+    float* err;
+    int64_t w_stride;     // elements between consecutive matrices of w / wq / err
+    int64_t comp_stride;  // elements between consecutive matrices of comp
+    int64_t state_stride; // elements between consecutive matrices of out_states
+    int ld;               // row pitch of w / wq / err
+    int comp_ld;          // row pitch of comp
+    int tiles_n;          // column tiles visited per matrix
+    const int* tile_map;  // optional: visited column tile i is tile_map[i] (mixed-rate maps)
+    float multiplier;
+    int rows_mode;
+};
+
+// Row-major offset (row * 16 + col) of tensor-core element t (exl3_encoder_backend.py:35-57).
+__device__ __forceinline__ int tensor_core_rc(int t, int& col)
+{
+    const int lane = t >> 3, j = t & 7;
+    const int r0 = (lane & 3) * 2;
+    const int row = r0 + (j & 1) + ((j & 2) ? 8 : 0);
+    col = (lane >> 2) + ((j & 4) ? 8 : 0);
+    return row;
+}
+
 template <int K, bool DEDICATED>
 __global__ void __launch_bounds__(kThreads, 1)
-viterbi_kernel(const float* __restrict__ tiles, float* __restrict__ out_tiles,
-               uint16_t* __restrict__ out_states, const uint8_t* __restrict__ lut_pm,
+viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
                const uint8_t* __restrict__ lut_state, uint8_t* scratch_base, int64_t n_tiles,
                int context)
 {
@@ -440,9 +475,32 @@ viterbi_kernel(const float* __restrict__ tiles, float* __restrict__ out_tiles,
         }
     }
 
+    // Offsets are recomputed after the search rather than kept live across it (registers).
+    auto locate = [&](int64_t tile, int64_t& w_off, int64_t& comp_off, int64_t& state_off) {
+        const int64_t b = tile / io.tiles_n;
+        int tn = int(tile - b * io.tiles_n);
+        if (io.tile_map != nullptr) tn = io.tile_map[tn];
+        int col;
+        const int row = tensor_core_rc(threadIdx.x, col);
+        w_off = b * io.w_stride + int64_t(row) * io.ld + tn * 16 + col;
+        comp_off = b * io.comp_stride + int64_t(row) * io.comp_ld + tn * 16 + col;
+        state_off = b * io.state_stride + int64_t(tn) * 256 + threadIdx.x;
+    };
+
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         if (threadIdx.x < 256) {
-            float w = tiles[tile * 256 + threadIdx.x];
+            float w;
+            if (io.rows_mode) {
+                int64_t w_off, comp_off, state_off;
+                locate(tile, w_off, comp_off, state_off);
+                w = io.w[w_off];
+                if (io.comp != nullptr && io.multiplier != 0.0f) {
+                    const float c = io.comp[comp_off];
+                    w = (io.multiplier == 1.0f) ? __fadd_rn(w, c) : __fadd_rn(w, __fmul_rn(io.multiplier, c));
+                }
+            } else {
+                w = io.tiles[tile * 256 + threadIdx.x];
+            }
             if constexpr (DEDICATED) w = fmaxf(-64.0f, fminf(w, 64.0f));  // k2 cuh:82-91
             sm->in_h[threadIdx.x] = __float2half_rn(w);
         }
@@ -455,8 +513,17 @@ viterbi_kernel(const float* __restrict__ tiles, float* __restrict__ out_tiles,
         }
         if (threadIdx.x < 256) {
             const uint16_t s = sm->states[threadIdx.x];
-            out_states[tile * 256 + threadIdx.x] = s;
-            out_tiles[tile * 256 + threadIdx.x] = e4m3_to_float(lut_state[s]);
+            const float q = e4m3_to_float(lut_state[s]);
+            if (io.rows_mode) {
+                int64_t w_off, comp_off, state_off;
+                locate(tile, w_off, comp_off, state_off);
+                io.out_states[state_off] = s;
+                io.wq[w_off] = q;
+                if (io.err != nullptr) io.err[w_off] = __fsub_rn(io.w[w_off], q);
+            } else {
+                io.out_states[tile * 256 + threadIdx.x] = s;
+                io.out_tiles[tile * 256 + threadIdx.x] = q;
+            }
         }
         __syncthreads();
     }
@@ -474,9 +541,8 @@ int resident_ctas()
 }
 
 template <int K, bool DEDICATED>
-int launch(const float* tiles, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
-           int context, float* out_tiles, int16_t* out_states, void* scratch, size_t scratch_bytes,
-           cudaStream_t stream)
+int launch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
+           int context, void* scratch, size_t scratch_bytes, cudaStream_t stream)
 {
     using G = Geo<K>;
     const int sms = resident_ctas();
@@ -490,8 +556,7 @@ int launch(const float* tiles, int64_t n_tiles, const uint8_t* lut_state, const 
                                            int(smem_bytes<K>()));
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaFuncSetAttribute(viterbi)");
     kernel<<<dim3(unsigned(grid)), dim3(kThreads), smem_bytes<K>(), stream>>>(
-        tiles, out_tiles, reinterpret_cast<uint16_t*>(out_states), lut_pm, lut_state,
-        static_cast<uint8_t*>(scratch), n_tiles, context);
+        io, lut_pm, lut_state, static_cast<uint8_t*>(scratch), n_tiles, context);
     err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "viterbi kernel launch");
     return QSRTB_OK;
@@ -545,10 +610,9 @@ extern "C" int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* by
     return QSRTB_OK;
 }
 
-extern "C" int qsrtb_quantize_tiles(const float* tiles, int64_t n_tiles, const uint8_t* lut_state,
-                                    const uint8_t* lut_pm, int bits, int tailbite_context,
-                                    int variant, float* out_tiles, int16_t* out_states,
-                                    void* scratch, size_t scratch_bytes, void* stream)
+namespace {
+
+int check_common(int bits, int tailbite_context, int variant, int64_t n_tiles)
 {
     if (bits < 2 || bits > 4) return qsrtb_fail(QSRTB_EINVAL, "bits must be 2, 3 or 4");
     if (tailbite_context < 1 || tailbite_context > 128)
@@ -556,22 +620,83 @@ extern "C" int qsrtb_quantize_tiles(const float* tiles, int64_t n_tiles, const u
     if (variant != 0 && !(variant == 1 && bits == 2))
         return qsrtb_fail(QSRTB_EINVAL, "variant 1 (dedicated K2 arithmetic) needs bits == 2");
     if (n_tiles < 0) return qsrtb_fail(QSRTB_EINVAL, "negative tile count");
-    if (n_tiles == 0) return QSRTB_OK;
-    if (!tiles || !lut_state || !lut_pm || !out_tiles || !out_states || !scratch)
-        return qsrtb_fail(QSRTB_EINVAL, "null pointer");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return QSRTB_OK;
+}
+
+int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
+             int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
+{
     switch (bits) {
         case 2:
             if (variant == 1)
-                return launch<2, true>(tiles, n_tiles, lut_state, lut_pm, tailbite_context, out_tiles,
-                                       out_states, scratch, scratch_bytes, s);
-            return launch<2, false>(tiles, n_tiles, lut_state, lut_pm, tailbite_context, out_tiles,
-                                    out_states, scratch, scratch_bytes, s);
+                return launch<2, true>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
+            return launch<2, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
         case 3:
-            return launch<3, false>(tiles, n_tiles, lut_state, lut_pm, tailbite_context, out_tiles,
-                                    out_states, scratch, scratch_bytes, s);
+            return launch<3, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
         default:
-            return launch<4, false>(tiles, n_tiles, lut_state, lut_pm, tailbite_context, out_tiles,
-                                    out_states, scratch, scratch_bytes, s);
+            return launch<4, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
     }
+}
+
+}  // namespace
+
+extern "C" int qsrtb_quantize_tiles(const float* tiles, int64_t n_tiles, const uint8_t* lut_state,
+                                    const uint8_t* lut_pm, int bits, int tailbite_context,
+                                    int variant, float* out_tiles, int16_t* out_states,
+                                    void* scratch, size_t scratch_bytes, void* stream)
+{
+    const int bad = check_common(bits, tailbite_context, variant, n_tiles);
+    if (bad) return bad;
+    if (n_tiles == 0) return QSRTB_OK;
+    if (!tiles || !lut_state || !lut_pm || !out_tiles || !out_states || !scratch)
+        return qsrtb_fail(QSRTB_EINVAL, "null pointer");
+    TileIO io{};
+    io.tiles = tiles;
+    io.out_tiles = out_tiles;
+    io.out_states = reinterpret_cast<uint16_t*>(out_states);
+    io.rows_mode = 0;
+    io.tiles_n = 1;
+    return dispatch(io, n_tiles, lut_state, lut_pm, bits, tailbite_context, variant, scratch,
+                    scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier,
+                                        int batch, int n, int ld, int comp_ld, int64_t w_stride,
+                                        int64_t comp_stride, const uint8_t* lut_state,
+                                        const uint8_t* lut_pm, int bits, int tailbite_context,
+                                        int variant, float* wq, float* err, int16_t* out_states,
+                                        int64_t state_stride, const int32_t* tile_map,
+                                        int tile_map_count, void* scratch, size_t scratch_bytes,
+                                        void* stream)
+{
+    if (batch < 0 || n < 0 || (n % 16) != 0) return qsrtb_fail(QSRTB_EINVAL, "n must be a multiple of 16");
+    if (tile_map && (tile_map_count < 0 || tile_map_count > n / 16))
+        return qsrtb_fail(QSRTB_EINVAL, "tile map longer than the row of tiles");
+    const int visited = tile_map ? tile_map_count : n / 16;
+    const int64_t n_tiles = int64_t(batch) * visited;
+    const int bad = check_common(bits, tailbite_context, variant, n_tiles);
+    if (bad) return bad;
+    if (n_tiles == 0) return QSRTB_OK;
+    if (!w || !wq || !out_states || !lut_state || !lut_pm || !scratch)
+        return qsrtb_fail(QSRTB_EINVAL, "null pointer");
+    if (ld < n || (comp && comp_ld < n)) return qsrtb_fail(QSRTB_EINVAL, "row pitch smaller than n");
+    if (!(multiplier >= 0.0f && multiplier <= 1.0f))
+        return qsrtb_fail(QSRTB_EINVAL, "ldlq feedback multiplier must be in [0, 1]");
+    TileIO io{};
+    io.w = w;
+    io.comp = comp;
+    io.wq = wq;
+    io.err = err;
+    io.out_states = reinterpret_cast<uint16_t*>(out_states);
+    io.w_stride = w_stride;
+    io.comp_stride = comp_stride;
+    io.state_stride = state_stride;
+    io.ld = ld;
+    io.comp_ld = comp_ld;
+    io.tiles_n = visited;
+    io.tile_map = tile_map;
+    io.multiplier = multiplier;
+    io.rows_mode = 1;
+    return dispatch(io, n_tiles, lut_state, lut_pm, bits, tailbite_context, variant, scratch,
+                    scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -1,0 +1,974 @@
+"""BlockLDLQ trellis encoder: the ``quantizer_module`` entry points on B200.
+
+Host-side mirror of the reference's encoder backend (``qsrt/exl3_encoder_backend.py``): the
+same function names, argument meaning, ``quant_args`` / ``H_data`` mutation contract and error
+behaviour, so a caller that holds the reference's ``quantizer_module`` can hold this module
+instead.  The numerical work is done by the hand-written kernels of ``libqsrt_b200.so``:
+
+* ``qsrtb_hadamard128``  - 128-point block Hadamards fused with the sign/scale vectors,
+* ``qsrtb_col_sumsq``    - out-channel RMS,
+* ``qsrtb_block_ldl_normalize`` - Cholesky factor -> block-LDL feedback factor,
+* ``qsrtb_ldlq_quantize_rows``  - one 16-row LDLQ step (feedback add, tile gather, Viterbi,
+  scatter) in a single launch,
+* ``qsrtb_quantize_tiles`` / ``qsrtb_pack_trellis``.
+
+PyTorch supplies device memory, streams, the seeded sign draws (which must come from torch's
+CUDA generator to match the reference, ``qsrt/rng.py:16-20``), the dense Cholesky and the
+plain feedback GEMMs (cuBLAS, the very calls the reference issues, which keeps the float32
+rounding of the feedback identical).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import threading
+
+import torch
+
+from . import _lib
+from .tiles import _stream_ptr, encode_tiles, prepared_table, quantize_tiles, traceback_scratch, K2_DEDICATED_MAX_LABEL
+
+had_k, had_n = 128, 128
+codebook_scale = 1.24371088
+SIGMA_REG = 0.025
+
+finalize_capture_H_mutex = threading.Lock()
+_SHARED_INPUT_SCALES: dict = {}
+
+
+# --------------------------------------------------------------------------------------
+# kernel wrappers
+# --------------------------------------------------------------------------------------
+
+def _hadamard(x: torch.Tensor, axis: int, scale: torch.Tensor | None = None, *, per_col: bool = False,
+              divide: bool = False, after: bool = False, row_sumsq: torch.Tensor | None = None) -> None:
+    """In-place blockwise Hadamard of a [rows, cols] or stacked [B, rows, cols] float32 tensor."""
+
+    if x.dtype != torch.float32 or not x.is_cuda:
+        raise TypeError("Hadamard input must be a CUDA float32 tensor")
+    if x.ndim == 2:
+        batch, (rows, cols) = 1, x.shape
+    elif x.ndim == 3:
+        batch, rows, cols = x.shape
+    else:
+        raise ValueError("Hadamard input must be a matrix or a stack of matrices")
+    if not x.is_contiguous():
+        raise ValueError("Hadamard input must be contiguous")
+    if scale is not None:
+        scale = scale.reshape(batch, -1)
+        if scale.dtype != torch.float32 or not scale.is_contiguous() or scale.device != x.device:
+            raise TypeError("scale vector must be contiguous float32 on the matrix device")
+        if scale.shape[1] != (cols if per_col else rows):
+            raise ValueError("scale vector length does not match the scaled axis")
+    with torch.cuda.device(x.device):
+        _lib.check(
+            _lib.lib().qsrtb_hadamard128(
+                x.data_ptr(), batch, rows, cols, cols, rows * cols, axis,
+                scale.data_ptr() if scale is not None else None,
+                scale.shape[1] if scale is not None else 0,
+                int(per_col), int(divide), int(after),
+                row_sumsq.data_ptr() if row_sumsq is not None else None, rows,
+                _stream_ptr(x.device),
+            ),
+            "qsrtb_hadamard128",
+        )
+
+
+def preapply_had_l(x: torch.Tensor, had_dim: int) -> torch.Tensor:
+    """``had @ x`` per block of 128 rows (exl3_encoder_backend.py:275-282), out of place."""
+
+    if had_dim != 128:
+        raise ValueError("the B200 encoder implements the 128-point block Hadamard")
+    out = x.to(torch.float32).contiguous().clone()
+    _hadamard(out, 0)
+    return out.to(x.dtype)
+
+
+def preapply_had_r(x: torch.Tensor, had_dim: int) -> torch.Tensor:
+    """``x @ had`` per block of 128 columns (exl3_encoder_backend.py:285-292), out of place."""
+
+    if had_dim != 128:
+        raise ValueError("the B200 encoder implements the 128-point block Hadamard")
+    out = x.to(torch.float32).contiguous().clone()
+    _hadamard(out, 1)
+    return out.to(x.dtype)
+
+
+def blockwise_preapply_had_l_(x: torch.Tensor, had_dim: int) -> None:
+    assert x.shape[0] % had_dim == 0 and x.dtype == torch.float and had_dim == 128
+    _hadamard(x, 0)
+
+
+def blockwise_preapply_had_r_(x: torch.Tensor, had_dim: int) -> None:
+    assert x.shape[1] % had_dim == 0 and x.dtype == torch.float and had_dim == 128
+    _hadamard(x, 1)
+
+
+def _col_sumsq(x: torch.Tensor) -> torch.Tensor:
+    rows, cols = x.shape
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    chunks = max(1, (rows + 255) // 256)
+    work = torch.empty(chunks * cols, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(
+            _lib.lib().qsrtb_col_sumsq(
+                x.data_ptr(), 1, rows, cols, cols, rows * cols, out.data_ptr(), cols,
+                work.data_ptr(), work.numel() * 4, _stream_ptr(x.device),
+            ),
+            "qsrtb_col_sumsq",
+        )
+    return out
+
+
+def seeded_normal(length: int, *, device: torch.device, seed: int | None) -> torch.Tensor:
+    """Device-local seeded normal draw (qsrt/rng.py:8-20)."""
+
+    generator = None
+    if seed is not None:
+        generator = torch.Generator(device=device)
+        generator.manual_seed(seed)
+    return torch.randn(length, device=device, generator=generator)
+
+
+def _signs(length: int, device: torch.device, seed: int | None) -> torch.Tensor:
+    return (seeded_normal(length, device=device, seed=seed).sign() + 1e-5).sign().to(torch.float)
+
+
+def output_signs(n: int, device: torch.device, quant_args: dict) -> torch.Tensor:
+    """exl3_encoder_backend.py:2562-2577."""
+
+    return _signs(n, device, quant_args.get("sv_seed")).unsqueeze(0)
+
+
+def make_shared_h(in_features: int, device: torch.device, hessian: torch.Tensor | None = None) -> dict:
+    """Mutable Hessian wrapper consumed by the encoder (qsrt/ldlq.py:11-36)."""
+
+    if hessian is None:
+        hessian = torch.eye(in_features, dtype=torch.float32)
+    if tuple(hessian.shape) != (in_features, in_features):
+        raise ValueError(f"Hessian shape {tuple(hessian.shape)} does not match {in_features}")
+    canonical = hessian.to(device=device, dtype=torch.float32, copy=True).contiguous()
+    return {
+        "H": canonical.clone(),
+        "error_H": canonical,
+        "first_key": f"h{in_features}",
+        "count": 1,
+        "finalized": False,
+        "num_total": 1,
+        "inf_nan": torch.zeros(2, dtype=torch.long, device=device),
+        "device": device,
+    }
+
+
+# --------------------------------------------------------------------------------------
+# H2: Hessian damping, congruence and block LDL
+# --------------------------------------------------------------------------------------
+
+def block_ldl(H: torch.Tensor, b: int, quant_args: dict, verbose: bool):
+    """Block LDL of a damped Hessian (exl3_encoder_backend.py:323-393).
+
+    Returns ``(L, H_cpu)``: ``L`` overwrites H's device storage; a failed Cholesky is retried
+    up to ten times with ``2 * sigma_reg * mean(diag)`` of extra damping, then re-raised.
+    """
+
+    if b != 16:
+        raise ValueError("the B200 encoder factors in 16x16 blocks")
+    n = H.shape[0]
+    assert n % b == 0
+    retries = 0
+    while True:
+        L, info = torch.linalg.cholesky_ex(H)
+        if int(info.item()) == 0:
+            break
+        retries += 1
+        if retries > 10:
+            print(" ## Cholesky decomp. failed, number of retries exceeded")
+            raise torch.linalg.LinAlgError(
+                f"linalg.cholesky: the input is not positive-definite (leading minor {int(info.item())})"
+            )
+        print(f" !! Cholesky decomp. failed, increasing diagonal damping, attempt {retries}/10")
+        H.diagonal().add_(2.0 * quant_args.get("sigma_reg", SIGMA_REG) * H.diagonal().mean())
+    H_cpu = H.cpu()
+    H.copy_(L)
+    del L
+    with torch.cuda.device(H.device):
+        _lib.check(
+            _lib.lib().qsrtb_block_ldl_normalize(H.data_ptr(), n, n, _stream_ptr(H.device)),
+            "qsrtb_block_ldl_normalize",
+        )
+    return H, H_cpu
+
+
+def _prepare_capture_H(H_data: dict, quant_args: dict, verbose: bool):
+    """Normalise and damp (exl3_encoder_backend.py:2077-2122); draws the input signs."""
+
+    H = H_data["H"]
+    count = H_data["count"]
+    if count == 0:
+        q_fallback = True
+        diag_mean = 0.0
+    else:
+        H /= count
+        diag_mean = torch.diag(H).mean()
+        q_fallback = diag_mean.item() < 1e-20
+    H.diagonal().add_(quant_args.get("sigma_reg", SIGMA_REG) * diag_mean)
+    diag = H.diagonal().clone()
+    su = _signs(H.shape[0], H.device, quant_args.get("seed")).unsqueeze(1)
+    H_data["su"] = su
+    H_data["diag"] = diag
+    H_data["q_fallback"] = q_fallback
+    return q_fallback, H, su, diag
+
+
+def _factor_capture_H(H_data: dict, H: torch.Tensor, su: torch.Tensor, quant_args: dict, verbose: bool):
+    """Decoder-input congruence and block factorisation (exl3_encoder_backend.py:2125-2160)."""
+
+    if su.shape != (H.shape[0], 1) or su.dtype != torch.float:
+        raise ValueError("input conditioning must be float32 [input, 1]")
+    if su.device != H.device:
+        su = su.to(H.device)
+    flat = su.reshape(-1).contiguous()
+    _hadamard(H, 1, flat, per_col=True)    # H *= su.T ; had_r
+    _hadamard(H, 0, flat, per_col=False)   # H *= su   ; had_l
+    q_fallback = bool(H_data["q_fallback"])
+    if q_fallback:
+        L = None
+    else:
+        L, H = block_ldl(H, 16, quant_args, verbose)
+    H_data["L"] = L
+    H = H.cpu()
+    H_data["H"] = H
+    H_data["su"] = su
+    H_data["finalized"] = True
+    return q_fallback, H, L, su, H_data["diag"]
+
+
+def prepare_capture_H_for_conditioning(H_data: dict, quant_args: dict, verbose: bool):
+    """First half of the two-stage preparation (exl3_encoder_backend.py:2163-2182)."""
+
+    with finalize_capture_H_mutex:
+        if H_data["H"].is_meta:
+            raise ValueError("conditioned QSRT requires a materialized dense Hessian")
+        if "H_swap_device" in H_data:
+            H_data["H"] = H_data["H"].to(H_data["H_swap_device"])
+            del H_data["H_swap_device"]
+        if H_data.get("_conditioning_pending"):
+            raise ValueError("conditioned Hessian preparation is already pending")
+        if H_data["finalized"]:
+            raise ValueError("conditioned QSRT Hessian was already finalized")
+        q_fallback, H, su, diag = _prepare_capture_H(H_data, quant_args, verbose)
+        H_data["_conditioning_pending"] = True
+        return q_fallback, H, su, diag
+
+
+def finalize_capture_H_with_conditioning(H_data: dict, su: torch.Tensor, quant_args: dict, verbose: bool):
+    """Second half: factor with regularize's complete ``su`` (exl3_encoder_backend.py:2185-2198)."""
+
+    with finalize_capture_H_mutex:
+        if not H_data.pop("_conditioning_pending", False):
+            raise ValueError("conditioned Hessian preparation was not started")
+        return _factor_capture_H(H_data, H_data["H"], su, quant_args, verbose)
+
+
+def finalize_capture_H(H_data: dict, quant_args: dict, verbose: bool):
+    """exl3_encoder_backend.py:2201-2243."""
+
+    with finalize_capture_H_mutex:
+        if H_data["H"].is_meta:
+            H_data["L"] = None
+            H_data["finalized"] = True
+            H_data["diag"] = None
+            H_data["q_fallback"] = True
+            su = _signs(H_data["H"].shape[0], torch.device(H_data["device"]), quant_args.get("seed")).unsqueeze(1)
+            H_data["su"] = su
+            return True, None, None, su, None
+        if "H_swap_device" in H_data:
+            H_data["H"] = H_data["H"].to(H_data["H_swap_device"])
+            del H_data["H_swap_device"]
+        H = H_data["H"]
+        if H_data["finalized"]:
+            return H_data["q_fallback"], H, H_data["L"], H_data["su"], H_data["diag"]
+        if H_data.get("_conditioning_pending"):
+            raise ValueError("cannot use ordinary finalization during QSRT conditioning")
+        q_fallback, H, su, _ = _prepare_capture_H(H_data, quant_args, verbose)
+        return _factor_capture_H(H_data, H, su, quant_args, verbose)
+
+
+# --------------------------------------------------------------------------------------
+# X1 / S1: tile order and global-scale search
+# --------------------------------------------------------------------------------------
+
+_perm_cache: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def tensor_core_perm(device) -> torch.Tensor:
+    """Row-major 16x16 tile -> tensor-core element order (exl3_encoder_backend.py:35-57)."""
+
+    key = str(device)
+    if key not in _perm_cache:
+        perm = [0] * 256
+        for lane in range(32):
+            r0 = (lane % 4) * 2
+            c0 = lane // 4
+            for j, row in enumerate((r0, r0 + 1, r0 + 8, r0 + 9)):
+                perm[lane * 8 + j] = row * 16 + c0
+                perm[lane * 8 + 4 + j] = row * 16 + c0 + 8
+        p = torch.tensor(perm, dtype=torch.int, device=device)
+        _perm_cache[key] = (p, torch.argsort(p))
+    return _perm_cache[key][0]
+
+
+def tensor_core_perm_i(device) -> torch.Tensor:
+    tensor_core_perm(device)
+    return _perm_cache[str(device)][1]
+
+
+def sample_scale_tiles(weight_r: torch.Tensor, width: int = 3) -> torch.Tensor:
+    """Tiles sampled for the global-scale search (exl3_encoder_backend.py:2383-2410): a
+    wrapped diagonal of the given width plus the tiles of highest and lowest RMS."""
+
+    device = weight_r.device
+    tiles_k = weight_r.shape[0] // 16
+    tiles_n = weight_r.shape[1] // 16
+    w4 = weight_r.view(tiles_k, 16, tiles_n, 16)
+    diag_len = max(tiles_k, tiles_n)
+    ii = torch.arange(diag_len, device=device).repeat_interleave(width)
+    ww = torch.arange(width, device=device).repeat(diag_len)
+    kk = ii % tiles_k
+    nn = (ii + ww) % tiles_n
+    num_x = max(8, (diag_len * width) // 16)
+    tile_ms = w4.square().mean(dim=(1, 3)).flatten()
+    num_x = min(num_x, (tile_ms.shape[0] + 1) // 2)
+    hi = torch.topk(tile_ms, num_x).indices
+    lo = torch.topk(tile_ms, num_x, largest=False).indices
+    xk = torch.cat((hi, lo)) // tiles_n
+    xn = torch.cat((hi, lo)) % tiles_n
+    tiles = w4[torch.cat((kk, xk)), :, torch.cat((nn, xn)), :].reshape(-1, 256)
+    return tiles[:, tensor_core_perm(device)].contiguous()
+
+
+def g_scale_search_batch(samples: list[torch.Tensor], quant_args: dict) -> list[tuple[float, torch.Tensor]]:
+    """Coarse grid, fine grid, parabolic refinement (exl3_encoder_backend.py:2413-2476).
+
+    Every (tensor, scale) evaluation of a stage goes through as few tile-encoder launches as
+    the 65,536-tile batch limit allows; the host synchronises twice per group.
+    """
+
+    n_t = len(samples)
+    device = samples[0].device
+    max_tiles = 65536
+
+    def eval_pairs(pairs, tile_sets):
+        out = torch.empty(len(pairs), dtype=torch.float, device=device)
+        i = 0
+        while i < len(pairs):
+            j, tot = i, 0
+            while j < len(pairs) and tot + tile_sets[pairs[j][0]].shape[0] <= max_tiles:
+                tot += tile_sets[pairs[j][0]].shape[0]
+                j += 1
+            j = max(j, i + 1)
+            batch = torch.cat([tile_sets[t] * s for t, s in pairs[i:j]])
+            quant_w, _ = quantize_tiles(batch, quant_args)
+            offset = 0
+            for p, (t, s) in enumerate(pairs[i:j]):
+                cnt = tile_sets[t].shape[0]
+                out[i + p] = (quant_w[offset:offset + cnt] / s - tile_sets[t]).square().mean()
+                offset += cnt
+            i = j
+        return out
+
+    coarse = [0.1 + 0.2 * i for i in range(10)]
+    subs = [s[::3] for s in samples]
+    pairs1 = [(t, s) for t in range(n_t) for s in coarse]
+    mse1 = eval_pairs(pairs1, subs).view(n_t, len(coarse))
+    centers = [coarse[c] for c in mse1.argmin(dim=1).tolist()]
+    step = 0.075
+    fine = [[c + step * (i - 2) for i in range(5)] for c in centers]
+    pairs2 = [(t, s) for t in range(n_t) for s in fine[t]]
+    mse2 = eval_pairs(pairs2, samples).view(n_t, 5)
+    mse2_h = mse2.tolist()
+    results = []
+    for t in range(n_t):
+        best = min(range(5), key=lambda i: mse2_h[t][i])
+        if 0 < best < 4:
+            y0, y1, y2 = mse2_h[t][best - 1], mse2_h[t][best], mse2_h[t][best + 1]
+            denom = y0 - 2.0 * y1 + y2
+            offset = 0.5 * (y0 - y2) / denom if denom > 0 else 0.0
+            offset = max(-0.5, min(0.5, offset))
+        else:
+            offset = 0.0
+        best_scale = max(fine[t][best] + offset * step, 0.01)
+        results.append((best_scale, mse2[t, best]))
+    return results
+
+
+def g_scale_gss(weight_r: torch.Tensor, verbose: bool, quant_args: dict, width: int = 3, pb=None):
+    """exl3_encoder_backend.py:2479-2505."""
+
+    tiles = sample_scale_tiles(weight_r, width)
+    best_scale, best_mse = g_scale_search_batch([tiles], quant_args)[0]
+    if verbose:
+        print(f"     - scale search: min = {best_scale:.6f}, mse: {best_mse.item():.6f}")
+    return best_scale, best_mse
+
+
+# --------------------------------------------------------------------------------------
+# R1: regularisation
+# --------------------------------------------------------------------------------------
+
+def apply_g_scale(weight, su, sv, g_scale: float, *, into_sv: bool = False):
+    """exl3_encoder_backend.py:2727-2751."""
+
+    if not math.isfinite(float(g_scale)) or float(g_scale) <= 0.0:
+        raise ValueError("g_scale must be positive and finite")
+    weight *= g_scale
+    if into_sv:
+        sv /= g_scale
+    else:
+        su /= g_scale
+    return weight, su, sv
+
+
+def relocate_g_scale_to_sv(su: torch.Tensor, sv: torch.Tensor, g_scale: float):
+    """exl3_encoder_backend.py:2711-2724."""
+
+    if not math.isfinite(float(g_scale)) or float(g_scale) <= 0.0:
+        raise ValueError("g_scale must be positive and finite")
+    return su * g_scale, sv / g_scale
+
+
+def regularize(weight: torch.Tensor, su: torch.Tensor, sv: torch.Tensor, quant_args: dict, verbose: bool,
+               H_diag: torch.Tensor | None, pb, skip_g_scale: bool = False, q_fallback: bool = False):
+    """Sign flips, channel scales, both Hadamards and the global scale
+    (exl3_encoder_backend.py:2580-2708).  ``weight`` [in, out] is transformed in place by two
+    fused kernels (divide-by-sv + output Hadamard + row sums; divide-by-su + input Hadamard)."""
+
+    force_out_scales = quant_args["apply_out_scales"]
+    if not q_fallback and H_diag is not None:
+        diag = H_diag.sqrt()
+        diag, _ = torch.sort(diag, descending=True)
+        cutoff = diag.shape[0] // 50
+        skew_factor = diag[:cutoff].sum() / diag.sum()
+        if verbose:
+            print(f"     - input state skew: {skew_factor.item():.6f}")
+        if force_out_scales is None:
+            apply_out_scales = skew_factor.item() < 0.15
+        else:
+            apply_out_scales = force_out_scales
+    else:
+        apply_out_scales = True if force_out_scales is None else force_out_scales
+    if q_fallback:
+        apply_out_scales = force_out_scales
+
+    k, n = weight.shape
+    out_channel_scales = (_col_sumsq(weight) / k).sqrt().unsqueeze(0)
+    mean = out_channel_scales.mean().item()
+    if mean > 1e-30:
+        out_channel_scales /= mean
+        quant_args["zeros"] = False
+    else:
+        quant_args["zeros"] = True
+        if force_out_scales is not None:
+            apply_out_scales = True
+    zero_out_scales = out_channel_scales.abs() < 1e-30
+    if apply_out_scales:
+        out_channel_scales[zero_out_scales] = 0.1
+        sv = (sv * out_channel_scales + 1e-10).float()
+
+    # weight /= sv ; output Hadamard ; per-input-channel sums of squares of the result
+    row_sumsq = torch.empty(k, dtype=torch.float32, device=weight.device)
+    _hadamard(weight, 1, sv.reshape(-1).contiguous(), per_col=True, divide=True, row_sumsq=row_sumsq)
+    sv[zero_out_scales] = 0.0
+
+    in_channel_scales = (row_sumsq / n).sqrt().unsqueeze(1)
+    in_channel_scales[in_channel_scales.abs() < 1e-30] = 0.1
+    shared_key = quant_args.get("shared_input_scales_key")
+    if shared_key is not None:
+        in_channel_scales = _SHARED_INPUT_SCALES.setdefault(shared_key, in_channel_scales)
+    su = (su * in_channel_scales / (-codebook_scale) + 1e-10).float()
+
+    # weight /= su ; input Hadamard
+    _hadamard(weight, 0, su.reshape(-1).contiguous(), per_col=False, divide=True)
+
+    if not skip_g_scale:
+        override = quant_args.get("g_scale_override")
+        if override is None:
+            g_scale, mse_scale = g_scale_gss(weight, False, quant_args, pb=pb)
+        else:
+            if isinstance(override, bool) or not isinstance(override, (int, float)):
+                raise TypeError("g_scale_override must be a real number")
+            g_scale = float(override)
+            if not math.isfinite(g_scale) or g_scale <= 0.0:
+                raise ValueError("g_scale_override must be positive and finite")
+            mse_scale = torch.tensor(float("nan"), device=weight.device)
+    else:
+        g_scale = 1.0
+    weight, su, sv = apply_g_scale(weight, su, sv, g_scale, into_sv=bool(quant_args.get("g_scale_into_sv")))
+    if verbose:
+        print(f"     - su/sv std: {su.std().item():.6f}   {sv.std().item():.6f}")
+        print(f"     - global scale: {g_scale:.6f}")
+        print(f"     - apply_out_scales: {str(apply_out_scales)}")
+    return apply_out_scales, weight, g_scale, su, sv
+
+
+# --------------------------------------------------------------------------------------
+# L1: BlockLDLQ feedback loop
+# --------------------------------------------------------------------------------------
+
+def _ldlq_feedback_multiplier(quant_args: dict) -> float:
+    value = quant_args.get("ldlq_feedback_multiplier", 1.0)
+    if (
+        isinstance(value, bool)
+        or not isinstance(value, (int, float))
+        or not math.isfinite(float(value))
+        or not 0.0 <= float(value) <= 1.0
+    ):
+        raise ValueError("ldlq_feedback_multiplier must be a real number in [0, 1]")
+    return float(value)
+
+
+def _codebook_for(quant_args: dict, bits: int) -> torch.Tensor:
+    codebook = quant_args.get("sqg_e4m3_lut")
+    by_bits = quant_args.get("sqg_e4m3_luts_by_bits")
+    if codebook is None and by_bits is not None:
+        if bits not in by_bits:
+            raise ValueError(f"missing rate-specific SQG K{bits} LUT")
+        codebook = by_bits[bits]
+    if codebook is None:
+        raise ValueError("the B200 encoder needs a QSRT table (sqg_e4m3_lut or sqg_e4m3_luts_by_bits)")
+    return codebook
+
+
+def _quantize_rows(w_rows, comp_rows, multiplier, wq_rows, err_rows, states_row, quant_args, bits,
+                   *, batch, n, ld, w_stride, comp_ld, comp_stride, state_stride, tile_map=None):
+    """One launch of ``qsrtb_ldlq_quantize_rows`` on views that start at the step's first row."""
+
+    device = w_rows.device
+    lut, lut_pm, abs_max = prepared_table(_codebook_for(quant_args, bits), bits, device)
+    dedicated = bits == 2 and abs_max == abs_max and 0.0 < abs_max <= K2_DEDICATED_MAX_LABEL
+    scratch = traceback_scratch(device, bits)
+    with torch.cuda.device(device):
+        _lib.check(
+            _lib.lib().qsrtb_ldlq_quantize_rows(
+                w_rows.data_ptr(), comp_rows.data_ptr() if comp_rows is not None else None,
+                float(multiplier), batch, n, ld, comp_ld, w_stride, comp_stride,
+                lut.data_ptr(), lut_pm.data_ptr(), bits, int(quant_args.get("tailbite_context", 128)),
+                1 if dedicated else 0, wq_rows.data_ptr(),
+                err_rows.data_ptr() if err_rows is not None else None,
+                states_row.data_ptr(), state_stride,
+                tile_map.data_ptr() if tile_map is not None else None,
+                tile_map.numel() if tile_map is not None else 0,
+                scratch.data_ptr(), scratch.numel(),
+                _stream_ptr(device),
+            ),
+            "qsrtb_ldlq_quantize_rows",
+        )
+
+
+def mixed_rate_spec(size_k: int, size_n: int, quant_args: dict):
+    """Validate a per-tile rate map (exl3_encoder_backend.py:737-772)."""
+
+    rate_axis = quant_args.get("mixed_rate_axis")
+    if rate_axis not in ("k", "n", "tile"):
+        raise ValueError("mixed_rate_axis must be 'k', 'n', or 'tile'")
+    if size_k % 16 or size_n % 16:
+        raise ValueError("mixed-rate LDLQ input must be 16x16 tile aligned")
+    raw_tile_bits = quant_args.get("mixed_tile_bits")
+    if raw_tile_bits is None:
+        raise ValueError("mixed_tile_bits is required for mixed-rate LDLQ")
+    tile_bits = tuple(raw_tile_bits)
+    if rate_axis == "tile":
+        rate_tiles = (size_k // 16) * (size_n // 16)
+    else:
+        rate_tiles = size_k // 16 if rate_axis == "k" else size_n // 16
+    if len(tile_bits) != rate_tiles:
+        raise ValueError(f"mixed_tile_bits has {len(tile_bits)} entries; expected {rate_tiles}")
+    if any(isinstance(bits, bool) or not isinstance(bits, int) or bits not in (1, 2, 3, 4) for bits in tile_bits):
+        raise ValueError("mixed-rate LDLQ supports only integer K1 through K4")
+    return rate_axis, tile_bits
+
+
+def _uniform_plan(bits: int):
+    return lambda row_tile: [(bits, None)]
+
+
+def _mixed_plan(size_k: int, size_n: int, quant_args: dict, device):
+    """Per row of tiles: [(bits, device list of column tiles or None for all)]."""
+
+    rate_axis, tile_bits = mixed_rate_spec(size_k, size_n, quant_args)
+    if quant_args.get("mixed_tile_codebook_ids") is not None or quant_args.get("sqg_e4m3_lut_banks_by_bits") is not None:
+        raise NotImplementedError("per-tile codebook banks are a research hook outside the B200 hot path")
+    if 1 in tile_bits:
+        raise NotImplementedError("K1 tiles are outside the B200 tile encoder (K2, K3, K4)")
+    tiles_n = size_n // 16
+
+    def positions(row_bits):
+        return [
+            (bits, torch.tensor([i for i, b in enumerate(row_bits) if b == bits], dtype=torch.int32, device=device))
+            for bits in sorted(set(row_bits))
+        ]
+
+    if rate_axis == "k":
+        return lambda row_tile: [(tile_bits[row_tile], None)]
+    if rate_axis == "n":
+        fixed = positions(tile_bits)
+        if len(fixed) == 1:
+            fixed = [(fixed[0][0], None)]
+        return lambda row_tile: fixed
+    cache: dict[tuple, list] = {}
+
+    def per_tile(row_tile):
+        row_bits = tuple(tile_bits[row_tile * tiles_n:(row_tile + 1) * tiles_n])
+        if row_bits not in cache:
+            cache[row_bits] = positions(row_bits)
+        return cache[row_bits]
+
+    return per_tile
+
+
+def _ldlq_core(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, pb=None):
+    """The reference's reverse block recursion (exl3_encoder_backend.py:470-539, 2020-2068):
+    spans of ``buf_size_k`` rows from the bottom up, 16-row blocks inside a span, the same
+    two GEMM calls, and one fused encode launch per rate present in the 16-row step."""
+
+    assert weights.ndim == 3 and Ls.ndim == 3
+    batch, size_k, size_n = weights.shape
+    assert size_k % 16 == 0 and size_n % 128 == 0
+    device = weights.device
+    multiplier = _ldlq_feedback_multiplier(quant_args)
+    buf_size_k = max(quant_args.get("buf_size_k", 128), 16)
+    assert buf_size_k % 16 == 0 and size_k % buf_size_k == 0
+    tiles_k, tiles_n = size_k // 16, size_n // 16
+
+    prod_cache = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
+    weight_q = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
+    err = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
+    encoded = torch.zeros((batch, tiles_k, tiles_n, 256), dtype=torch.short, device=device)
+    allow_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = bool(quant_args.get("ldlq_tf32", False))
+    try:
+        p_row = 0
+        for j in range(size_k, 0, -buf_size_k):
+            i = j - buf_size_k
+            for bj in range(buf_size_k, 0, -16):
+                bi = bj - 16
+                comp = prod_cache[:, i + bi:i + bj]
+                if bj < buf_size_k:
+                    # compensation from the rows already encoded inside this span
+                    comp.baddbmm_(Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
+                for bits, tile_map in plan((i + bi) // 16):
+                    _quantize_rows(
+                        weights[:, i + bi:], comp, multiplier, weight_q[:, i + bi:], err[:, i + bi:],
+                        encoded[:, (i + bi) // 16], quant_args, bits,
+                        batch=batch, n=size_n, ld=size_n, w_stride=size_k * size_n,
+                        comp_ld=size_n, comp_stride=size_k * size_n,
+                        state_stride=tiles_k * tiles_n * 256, tile_map=tile_map,
+                    )
+                if pb:
+                    p_row += 1
+                    pb.update(p_row)
+            if i > 0:
+                # cache the span's error for every row block still to be encoded
+                prod_cache[:, :i].baddbmm_(Ls[:, i:j, :i].transpose(1, 2), err[:, i:j])
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = allow_tf32
+    return weight_q, encoded
+
+
+def ldlq_batched(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, pb=None):
+    """LDLQ over a stack of same-shape tensors with per-tensor L
+    (exl3_encoder_backend.py:1980-2071): every 16-row step encodes all tensors' tiles in one
+    launch.  Returns (weight_q [B, k, n], encoded [B, k/16, n/16, 256])."""
+
+    return _ldlq_core(weights, Ls, quant_args, _uniform_plan(int(quant_args["K"])), pb)
+
+
+def ldlq_mixed(weight: torch.Tensor, L: torch.Tensor, quant_args: dict, pb=None):
+    """Dense-H LDLQ with the rate chosen per tile on one matrix axis
+    (exl3_encoder_backend.py:898-1082).  One traversal; a step launches once per rate present."""
+
+    size_k, size_n = weight.shape
+    plan = _mixed_plan(size_k, size_n, quant_args, weight.device)
+    weight_q, encoded = _ldlq_core(weight.unsqueeze(0), L.unsqueeze(0), quant_args, plan, pb)
+    return weight_q[0], encoded[0]
+
+
+def ldlq(weight: torch.Tensor, L: torch.Tensor, quant_args: dict, pb=None):
+    """exl3_encoder_backend.py:420-539: returns (weight_q [k, n], encoded [k/16, n/16, 256])."""
+
+    weight_q, encoded = ldlq_batched(weight.unsqueeze(0), L.unsqueeze(0), quant_args, pb)
+    return weight_q[0], encoded[0]
+
+
+def fallback_quant(weight: torch.Tensor, device, quant_args: dict, pb=None):
+    """Plain tile-by-tile encode without feedback, used when the Hessian is unusable
+    (exl3_encoder_backend.py:1833-1948).  Returns (weight_q, encoded, mse)."""
+
+    size_k, size_n = weight.shape
+    zero = torch.zeros((1, 1, 1), dtype=torch.float, device=weight.device)
+    args = dict(quant_args)
+    args["ldlq_feedback_multiplier"] = 0.0
+    bits = int(quant_args["K"])
+    weight_q = torch.zeros_like(weight)
+    encoded = torch.zeros((size_k // 16, size_n // 16, 256), dtype=torch.short, device=weight.device)
+    for row in range(0, size_k, 16):
+        _quantize_rows(
+            weight[row:], None, 0.0, weight_q[row:], None, encoded[row // 16], args, bits,
+            batch=1, n=size_n, ld=size_n, w_stride=0, comp_ld=size_n, comp_stride=0, state_stride=0,
+        )
+    del zero
+    mse = (weight - weight_q).square().mean().item() / max(weight.square().mean().item(), 1e-20)
+    return weight_q, encoded, mse
+
+
+def block_trace_parts(A, B, block_size=1024):
+    """Column-block terms of trace(A.T @ B @ A) (exl3_encoder_backend.py:1951-1964)."""
+
+    return torch.stack(
+        [
+            torch.einsum(
+                "ik,ij,jk->",
+                A,
+                B[:, j_start:min(j_start + block_size, B.shape[1])],
+                A[j_start:min(j_start + block_size, B.shape[1]), :],
+            )
+            for j_start in range(0, B.shape[1], block_size)
+        ]
+    )
+
+
+def block_trace(A, B, block_size=1024):
+    """exl3_encoder_backend.py:1967-1977."""
+
+    total = 0.0
+    for partial in block_trace_parts(A, B, block_size).cpu():
+        total += partial.item()
+    return total
+
+
+def pack_trellis(encoded: torch.Tensor, quant_args: dict) -> torch.Tensor:
+    """States [K/16, N/16, 256] -> packed words [K/16, N/16, 16*K] (exl3_encoder_backend.py:2361-2372)."""
+
+    K = quant_args["K"]
+    shape = encoded.shape
+    assert len(shape) == 3 and shape[2] == 256
+    assert encoded.dtype == torch.int16
+    encoded = encoded.contiguous()
+    packed = torch.empty((shape[0], shape[1], 256 * K // 16), dtype=torch.int16, device=encoded.device)
+    with torch.cuda.device(encoded.device):
+        _lib.check(
+            _lib.lib().qsrtb_pack_trellis(
+                encoded.data_ptr(), shape[0] * shape[1], int(K), packed.data_ptr(), _stream_ptr(encoded.device)
+            ),
+            "qsrtb_pack_trellis",
+        )
+    return packed
+
+
+# --------------------------------------------------------------------------------------
+# Entry points of the quantizer_module boundary
+# --------------------------------------------------------------------------------------
+
+_OUT_OF_SCOPE_ARGS = {
+    "output_hessian": "two-sided (output-Hessian) feedback",
+    "use_two_sided_traversal_without_output_feedback": "two-sided traversal controls",
+    "periodic_rate_schedules": "periodic (within-tile variable) rates",
+    "mcg": "the procedural MCG codebook",
+    "mul1": "the procedural MUL1 codebook",
+}
+
+
+def _reject_out_of_scope(quant_args: dict) -> None:
+    for key, what in _OUT_OF_SCOPE_ARGS.items():
+        if quant_args.get(key):
+            raise NotImplementedError(f"{what} is a research arm outside the B200 encoder hot path")
+    if int(quant_args.get("h2_viterbi_refine_sweeps", 0) or 0) > 0:
+        raise NotImplementedError("dense-H path refinement sweeps are not part of the B200 hot path yet")
+
+
+def _deregularize(weight_q: torch.Tensor, su: torch.Tensor, sv: torch.Tensor) -> torch.Tensor:
+    """had_l, *su, had_r, *sv (exl3_encoder_backend.py:3030-3034) with the scales fused."""
+
+    out = weight_q.contiguous().clone()
+    _hadamard(out, 0, su.reshape(-1).float().contiguous(), per_col=False, after=True)
+    _hadamard(out, 1, sv.reshape(-1).float().contiguous(), per_col=True, after=True)
+    return out
+
+
+def quantize_qsrt(weight: torch.Tensor, H_data: dict, quant_args: dict, return_weight_q: bool,
+                  progress_str: str | None = None, verbose: bool = False,
+                  swap_to_device: torch.device | None = None, save_reg: str | None = None):
+    """Encode one ``[in_features, out_features]`` float32 matrix
+    (exl3_encoder_backend.py:2754-3073).
+
+    Returns ``(weight_q, proxy_err, out_tensors)`` with ``out_tensors = {"suh", "svh",
+    "trellis"}``; ``weight`` is transformed in place, ``H_data`` gains ``L``/``su``/``diag``/
+    ``q_fallback``/``finalized`` and ``quant_args`` gains ``apply_out_scales``/``g_scale``/
+    ``q_fallback``/``zeros``/``h2_viterbi_refine_receipt`` exactly as in the reference.
+    """
+
+    _reject_out_of_scope(quant_args)
+    assert weight.dtype == torch.float
+    devices = quant_args["devices"]
+    if weight.device != torch.device(devices[0]):
+        weight = weight.to(devices[0])
+    device = weight.device if swap_to_device is None else swap_to_device
+    k, n = weight.shape
+
+    q_fallback, H, L, su, H_diag = finalize_capture_H(H_data, quant_args, verbose)
+    if L is not None:
+        L = L.to(device)
+    su = su.to(device)
+    if H_diag is not None:
+        H_diag = H_diag.to(device)
+    sv = output_signs(n, device, quant_args)
+    if H_data["L"] is not None:
+        H_data["L"] = H_data["L"].cpu()
+    if swap_to_device is not None:
+        weight = weight.to(swap_to_device)
+    weight_r = weight
+    del weight
+
+    apply_out_scales, weight_r, g_scale, su, sv = regularize(
+        weight_r, su, sv, quant_args, verbose, H_diag, None, q_fallback=q_fallback
+    )
+
+    mixed_rate = "mixed_rate_axis" in quant_args or "mixed_tile_bits" in quant_args
+    if not q_fallback:
+        if mixed_rate:
+            weight_q, encoded_q = ldlq_mixed(weight_r, L, quant_args)
+        else:
+            weight_q, encoded_q = ldlq(weight_r, L, quant_args)
+        del L
+        quant_args["h2_viterbi_refine_receipt"] = {"enabled": False, "reason": "disabled", "sweeps": []}
+    else:
+        if mixed_rate:
+            raise ValueError("variable-rate quantization requires a non-fallback dense Hessian")
+        weight_q, encoded_q, mse_err = fallback_quant(weight_r, device, quant_args)
+
+    if not q_fallback:
+        Hd = H.to(device)
+        num = block_trace(weight_r - weight_q, Hd)
+        den = block_trace(weight_r, Hd)
+        del Hd
+        proxy_err = num / max(den, 1e-8)
+    else:
+        proxy_err = mse_err
+
+    if return_weight_q or verbose:
+        weight_q = _deregularize(weight_q.to(device), su, sv)
+
+    suh = su.flatten().contiguous().to(dtype=torch.half, copy=True)
+    svh = sv.flatten().contiguous().to(dtype=torch.half, copy=True)
+    pack_trellis_fn = quant_args.get("pack_trellis_fn", pack_trellis)
+    trellis = pack_trellis_fn(encoded_q.to(device), quant_args)
+    out_tensors = {"suh": suh, "svh": svh, "trellis": trellis}
+    quant_args.update({"apply_out_scales": apply_out_scales, "g_scale": g_scale, "q_fallback": q_fallback})
+    return weight_q, proxy_err, out_tensors
+
+
+def quantize_uniform_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_args_list: list[dict],
+                           progress_str: str | None = None, verbose: bool = False):
+    """Encode a group of same-K matrices together (exl3_encoder_backend.py:3397-3620).
+
+    Shared Hessian (the same ``H_data`` object for every tensor): the regularised weights are
+    concatenated along out_features and run through one LDLQ pass.  Distinct Hessians over
+    same-shape tensors: the tensors are stacked and every 16-row step encodes all of their
+    tiles in one launch.  Returns ``[(proxy_err, out_tensors), ...]``.
+    """
+
+    if any("mixed_rate_axis" in qa or "mixed_tile_bits" in qa for qa in quant_args_list):
+        raise ValueError("mixed-rate LDLQ is currently supported by quantize_qsrt, not the same-K batch API")
+    for qa in quant_args_list:
+        _reject_out_of_scope(qa)
+    n_t = len(weights)
+    qa0 = quant_args_list[0]
+    device = torch.device(qa0["devices"][0])
+    shared_H = all(hd is H_datas[0] for hd in H_datas)
+    assert shared_H or all(w.shape == weights[0].shape for w in weights)
+    assert all(w.shape[0] == weights[0].shape[0] for w in weights)
+    assert all(qa["K"] == qa0["K"] for qa in quant_args_list)
+    results: list = [None] * n_t
+
+    finalized, batch_idx = [], []
+    for t in range(n_t):
+        q_fallback, H, L, su, H_diag = finalize_capture_H(H_datas[t], quant_args_list[t], verbose)
+        if q_fallback:
+            finalized.append(None)
+        else:
+            finalized.append((H, L, su, H_diag))
+            batch_idx.append(t)
+    for t in range(n_t):
+        if finalized[t] is None:
+            results[t] = quantize_qsrt(weights[t], H_datas[t], quant_args_list[t], False, None, verbose)[1:]
+    if not batch_idx:
+        return results
+
+    regs = {}
+    for t in batch_idx:
+        qa = quant_args_list[t]
+        H, L, su, H_diag = finalized[t]
+        weight = weights[t]
+        if weight.device != device:
+            weight = weight.to(device)
+        su = su.to(device)
+        if H_diag is not None:
+            H_diag = H_diag.to(device)
+        sv = output_signs(weight.shape[1], device, qa)
+        apply_out_scales, weight_r, _, su, sv = regularize(weight, su, sv, qa, verbose, H_diag, None, skip_g_scale=True)
+        regs[t] = [weight_r, su, sv, apply_out_scales]
+        weights[t] = None
+
+    samples = [sample_scale_tiles(regs[t][0]) for t in batch_idx]
+    scales = g_scale_search_batch(samples, qa0)
+    del samples
+    g_scales = {}
+    for t, (g_scale, _) in zip(batch_idx, scales):
+        regs[t][0] *= g_scale
+        if quant_args_list[t].get("g_scale_into_sv"):
+            regs[t][2] /= g_scale
+        else:
+            regs[t][1] /= g_scale
+        g_scales[t] = g_scale
+
+    if shared_H:
+        L = finalized[batch_idx[0]][1].to(device)
+        widths = [regs[t][0].shape[1] for t in batch_idx]
+        weight_r_cat = torch.cat([regs[t][0] for t in batch_idx], dim=1)
+        for t in batch_idx:
+            regs[t][0] = None
+        weight_q_cat, encoded_cat = ldlq(weight_r_cat, L, qa0)
+        del L
+        weight_rs = list(torch.split(weight_r_cat, widths, dim=1))
+        weight_qs = list(torch.split(weight_q_cat, widths, dim=1))
+        encodeds = list(torch.split(encoded_cat, [w // 16 for w in widths], dim=1))
+    else:
+        Ls = torch.stack([finalized[t][1].to(device) for t in batch_idx])
+        weight_r_stack = torch.stack([regs[t][0] for t in batch_idx])
+        for t in batch_idx:
+            regs[t][0] = None
+        weight_q_stack, encoded_stack = ldlq_batched(weight_r_stack, Ls, qa0)
+        del Ls
+        weight_rs = list(weight_r_stack.unbind(0))
+        weight_qs = list(weight_q_stack.unbind(0))
+        encodeds = list(encoded_stack.unbind(0))
+
+    Hd = None
+    for bi, t in enumerate(batch_idx):
+        qa = quant_args_list[t]
+        _, su, sv, apply_out_scales = regs[t]
+        if not shared_H or Hd is None:
+            Hd = finalized[t][0].to(device)
+        num = block_trace(weight_rs[bi] - weight_qs[bi], Hd)
+        den = block_trace(weight_rs[bi], Hd)
+        proxy_err = num / max(den, 1e-8)
+        weight_rs[bi] = None
+        weight_qs[bi] = None
+        suh = su.flatten().contiguous().to(dtype=torch.half, copy=True)
+        svh = sv.flatten().contiguous().to(dtype=torch.half, copy=True)
+        trellis = pack_trellis(encodeds[bi].contiguous(), qa)
+        encodeds[bi] = None
+        qa.update({"apply_out_scales": apply_out_scales, "g_scale": g_scales[t], "q_fallback": False})
+        results[t] = (proxy_err, {"suh": suh, "svh": svh, "trellis": trellis})
+    return results

@@ -1,0 +1,159 @@
+"""Calibration Hessians from routed activation rows.
+
+Mirrors ``qsrt/candidate_hessian.py`` (``weighted_covariance``, ``shrink_covariance``,
+``weighted_effective_sample_size``, ``adaptive_identity_shrinkage``) and the accumulator of
+``qsrt/capture.py:714-731``.  The contraction runs in ``qsrtb_hessian_accumulate`` (weighted
+lower-triangular SYRK, float32 accumulation); the scalar shrinkage statistics stay on the host
+in float64 exactly as in the reference.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .tiles import _stream_ptr
+
+
+def accumulate_hessian(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *, accumulate: bool = True) -> None:
+    """``lower (+)= sum_r w_r x_r x_r^T`` on the lower triangle of a CUDA float32 matrix."""
+
+    if lower.ndim != 2 or lower.shape[0] != lower.shape[1] or lower.dtype != torch.float32 or not lower.is_cuda:
+        raise ValueError("the accumulator must be a square CUDA float32 matrix")
+    if not lower.is_contiguous():
+        raise ValueError("the accumulator must be contiguous")
+    if rows.ndim != 2 or rows.shape[1] != lower.shape[0]:
+        raise ValueError("invalid covariance sample shapes")
+    rows = rows.to(device=lower.device, dtype=torch.float32).contiguous()
+    if weights is not None:
+        if weights.ndim != 1 or weights.shape[0] != rows.shape[0]:
+            raise ValueError("invalid covariance sample shapes")
+        weights = weights.to(device=lower.device, dtype=torch.float32).contiguous()
+    d = lower.shape[0]
+    with torch.cuda.device(lower.device):
+        _lib.check(
+            _lib.lib().qsrtb_hessian_accumulate(
+                rows.data_ptr(), weights.data_ptr() if weights is not None else None, rows.shape[0], d, d,
+                lower.data_ptr(), d, int(accumulate), _stream_ptr(lower.device),
+            ),
+            "qsrtb_hessian_accumulate",
+        )
+
+
+def finish_hessian(lower: torch.Tensor, weight_sum: float) -> torch.Tensor:
+    """Divide by the weight sum and mirror the triangle (in place); returns ``lower``."""
+
+    d = lower.shape[0]
+    with torch.cuda.device(lower.device):
+        _lib.check(
+            _lib.lib().qsrtb_hessian_finish(lower.data_ptr(), d, d, float(weight_sum), _stream_ptr(lower.device)),
+            "qsrtb_hessian_finish",
+        )
+    return lower
+
+
+def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: torch.device,
+                        chunk_rows: int = 65536, return_cpu: bool = True) -> tuple[torch.Tensor, float]:
+    """Return ``sum(w * x xT) / sum(w)`` as symmetric FP32 (qsrt/candidate_hessian.py:70-112).
+
+    ``chunk_rows`` only bounds the staging copy of host-resident rows; the kernel streams any
+    number of rows in one launch.
+    """
+
+    if rows.ndim != 2 or weights.ndim != 1 or rows.shape[0] != weights.shape[0]:
+        raise ValueError("invalid covariance sample shapes")
+    if not rows.shape[0] or not rows.shape[1]:
+        raise ValueError("covariance samples must be nonempty")
+    if chunk_rows <= 0:
+        raise ValueError("chunk_rows must be positive")
+    if not torch.all(torch.isfinite(rows)) or not torch.all(torch.isfinite(weights)):
+        raise ValueError("covariance samples must be finite")
+    if torch.any(weights < 0):
+        raise ValueError("covariance weights must be nonnegative")
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise ValueError("the B200 Hessian path requires a CUDA device")
+    dimension = int(rows.shape[1])
+    denominator = float(weights.double().sum())
+    if not math.isfinite(denominator) or denominator <= 0:
+        raise ValueError("covariance weights must have a positive finite sum")
+    accumulator = torch.empty((dimension, dimension), dtype=torch.float32, device=device)
+    first = True
+    for begin in range(0, int(rows.shape[0]), chunk_rows):
+        accumulate_hessian(accumulator, rows[begin:begin + chunk_rows], weights[begin:begin + chunk_rows], accumulate=not first)
+        first = False
+    covariance = finish_hessian(accumulator, denominator)
+    if return_cpu:
+        covariance = covariance.cpu()
+    if not torch.all(torch.isfinite(covariance)):
+        raise ValueError("weighted covariance is non-finite")
+    return covariance, denominator
+
+
+def shrink_covariance(global_covariance: torch.Tensor, local_covariance: torch.Tensor, alpha: float) -> torch.Tensor:
+    """Convex blend toward a global covariance (qsrt/candidate_hessian.py:115-140)."""
+
+    alpha = float(alpha)
+    if not math.isfinite(alpha) or not 0.0 <= alpha <= 1.0:
+        raise ValueError("alpha must be finite and in [0, 1]")
+    if (global_covariance.ndim != 2 or global_covariance.shape[0] != global_covariance.shape[1]
+            or local_covariance.shape != global_covariance.shape):
+        raise ValueError("global and local covariances must be equal-size squares")
+    if not torch.all(torch.isfinite(global_covariance)) or not torch.all(torch.isfinite(local_covariance)):
+        raise ValueError("covariances must be finite")
+    blended = torch.lerp(global_covariance.float(), local_covariance.float(), alpha)
+    return ((blended + blended.T) * 0.5).contiguous()
+
+
+def weighted_effective_sample_size(weights: torch.Tensor) -> float:
+    """Kish effective sample size (qsrt/candidate_hessian.py:143-153)."""
+
+    if weights.ndim != 1 or not weights.numel():
+        raise ValueError("weights must be a nonempty vector")
+    if not torch.all(torch.isfinite(weights)) or torch.any(weights < 0):
+        raise ValueError("weights must be finite and nonnegative")
+    weights64 = weights.double()
+    total = weights64.sum()
+    squared_total = weights64.square().sum()
+    if total <= 0 or squared_total <= 0:
+        raise ValueError("weights must have positive effective support")
+    return float(total.square() / squared_total)
+
+
+def adaptive_identity_shrinkage(local_covariance: torch.Tensor, weights: torch.Tensor, *,
+                                max_local_alpha: float = 0.75) -> tuple[torch.Tensor, dict[str, float]]:
+    """OAS shrinkage toward the scaled identity with Kish n_eff (qsrt/candidate_hessian.py:156-216)."""
+
+    max_local_alpha = float(max_local_alpha)
+    if not math.isfinite(max_local_alpha) or not 0.0 <= max_local_alpha <= 1.0:
+        raise ValueError("max_local_alpha must be finite and in [0, 1]")
+    if local_covariance.ndim != 2 or local_covariance.shape[0] != local_covariance.shape[1]:
+        raise ValueError("local covariance must be square")
+    if not torch.all(torch.isfinite(local_covariance)):
+        raise ValueError("local covariance must be finite")
+    effective_rows = weighted_effective_sample_size(weights)
+    dimension = int(local_covariance.shape[0])
+    local64 = local_covariance.double()
+    local_trace = torch.trace(local64)
+    if local_trace <= 0:
+        raise ValueError("local covariance trace must be positive")
+    mu = local_trace / dimension
+    mean_square = local64.square().mean()
+    denominator = (effective_rows + 1.0) * (mean_square - mu.square() / dimension)
+    if denominator <= 0:
+        oas_shrinkage = 1.0
+    else:
+        oas_shrinkage = min(1.0, max(0.0, float((mean_square + mu.square()) / denominator)))
+    local_alpha = min(max_local_alpha, 1.0 - oas_shrinkage)
+    identity_scale = float(mu)
+    scaled_identity = torch.eye(dimension, dtype=torch.float32, device=local_covariance.device).mul_(identity_scale)
+    blended = shrink_covariance(scaled_identity, local_covariance, local_alpha)
+    return blended, {
+        "effective_sample_size": effective_rows,
+        "oas_shrinkage": oas_shrinkage,
+        "local_alpha": local_alpha,
+        "max_local_alpha": max_local_alpha,
+        "identity_scale": identity_scale,
+    }
