@@ -32,6 +32,11 @@ extern "C" {
 int qsrtb_abi_version(void);
 const char* qsrtb_last_error(void);
 
+/* Measurement aid (no reference counterpart): runs iters x 8 independent half2 FMAs per thread
+ * on a device-filling grid; *fma_lanes (HOST pointer) receives the number of half lanes
+ * issued.  Timed by the benchmark to obtain the half2 FMA rate used as ALU roofline. */
+int qsrtb_probe_half2_fma(int iters, float* sink, double* fma_lanes, void* stream);
+
 /* ---- V5: look-up table preparation -------------------------------------------------
  * Replaces the table transpose of qsrt/sqg_quantizer.py:611-640.
  * lut_state : 65,536 E4M3 bytes indexed by the 16-bit trellis state.

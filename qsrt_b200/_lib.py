@@ -19,6 +19,7 @@ _PTR = _c.c_void_p
 _SIGNATURES = {
     "qsrtb_abi_version": (_c.c_int, []),
     "qsrtb_last_error": (_c.c_char_p, []),
+    "qsrtb_probe_half2_fma": (_c.c_int, [_c.c_int, _PTR, _c.POINTER(_c.c_double), _PTR]),
     "qsrtb_lut_prepare": (_c.c_int, [_PTR, _c.c_int, _PTR, _PTR, _PTR]),
     "qsrtb_viterbi_scratch_bytes": (_c.c_int, [_c.c_int, _c.c_int64, _c.POINTER(_c.c_size_t)]),
     "qsrtb_quantize_tiles": (
@@ -56,8 +57,46 @@ def exported_symbols() -> tuple[str, ...]:
     return tuple(_SIGNATURES)
 
 
+# Kernel launches issued by one call of each entry point (0 = host only).
+_KERNELS_PER_CALL = {
+    "qsrtb_abi_version": 0,
+    "qsrtb_last_error": 0,
+    "qsrtb_viterbi_scratch_bytes": 0,
+    "qsrtb_col_sumsq": 2,
+    "qsrtb_block_ldl_normalize": 2,
+}
+launch_counts: dict[str, int] = {}
+
+
+def kernel_launches() -> int:
+    """Kernels of this library launched so far by this process."""
+
+    return sum(launch_counts.values())
+
+
+class _Counted:
+    """The loaded library with per-entry-point launch accounting."""
+
+    def __init__(self, handle: ctypes.CDLL) -> None:
+        self._handle = handle
+        for name in _SIGNATURES:
+            setattr(self, name, self._wrap(name, getattr(handle, name)))
+
+    @staticmethod
+    def _wrap(name, fn):
+        per_call = _KERNELS_PER_CALL.get(name, 1)
+        if per_call == 0:
+            return fn
+
+        def counted(*args):
+            launch_counts[name] = launch_counts.get(name, 0) + per_call
+            return fn(*args)
+
+        return counted
+
+
 @lru_cache(maxsize=1)
-def lib() -> ctypes.CDLL:
+def lib() -> "_Counted":
     if not LIBRARY.exists():
         raise RuntimeError(
             f"{LIBRARY} is missing: build it with `python -m qsrt_b200.build` "
@@ -68,7 +107,7 @@ def lib() -> ctypes.CDLL:
         fn = getattr(handle, name)
         fn.restype = restype
         fn.argtypes = argtypes
-    return handle
+    return _Counted(handle)
 
 
 def check(status: int, what: str) -> None:

@@ -27,6 +27,7 @@ import threading
 import torch
 
 from . import _lib
+from . import tiles as _tiles
 from .tiles import _stream_ptr, encode_tiles, prepared_table, quantize_tiles, traceback_scratch, K2_DEDICATED_MAX_LABEL
 
 had_k, had_n = 128, 128
@@ -548,7 +549,8 @@ def _quantize_rows(w_rows, comp_rows, multiplier, wq_rows, err_rows, states_row,
     lut, lut_pm, abs_max = prepared_table(_codebook_for(quant_args, bits), bits, device)
     dedicated = bits == 2 and abs_max == abs_max and 0.0 < abs_max <= K2_DEDICATED_MAX_LABEL
     scratch = traceback_scratch(device, bits)
-    with torch.cuda.device(device):
+    visited = tile_map.numel() if tile_map is not None else n // 16
+    with torch.cuda.device(device), _tiles.timed_search(device, batch * visited, bits):
         _lib.check(
             _lib.lib().qsrtb_ldlq_quantize_rows(
                 w_rows.data_ptr(), comp_rows.data_ptr() if comp_rows is not None else None,

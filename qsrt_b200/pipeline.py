@@ -1,0 +1,188 @@
+"""Expert-level orchestration of the encoder hot path.
+
+One gated expert is three matrices: ``w1`` (gate) and ``w3`` (up), both ``[intermediate,
+hidden]``, and ``w2`` (down) ``[hidden, intermediate]``.  Following the reference's
+whole-expert flow (``qsrt/pack/qsrt_candidates.py:1258-1375`` and, for the GLM variant,
+``qsrt/glm52_down_construction.py:159-260``):
+
+1. ``H13`` = gate^2-weighted covariance of the routed input rows (``build_expert_hessians``,
+   ``qsrt/qsrt_candidates.py:534-618``);
+2. ``w1`` and ``w3`` share ``H13`` and are encoded together (one LDLQ pass over their
+   concatenated output channels, ``quantize_uniform_batch``);
+3. the middle activation ``act(x w1^T) * (x w3^T)`` of the routed rows - from the source
+   weights or from the just-encoded reconstructions - gives ``H2`` with OAS shrinkage;
+4. ``w2`` is encoded against ``H2`` (experts of a batch stacked, one launch per 16-row step);
+5. the routed functional error ``sum_rows gate^2 * ||y_hat - y||^2`` scores the candidate
+   (``functional_sse_by_request``, ``qsrt/qsrt_candidates.py:621-654``);
+6. payloads are packed; decoding them back to E4M3 must reproduce the encoder's states.
+
+Everything stays on the device; the only host synchronisations are the ones the reference
+also has (scale search, Cholesky status, proxy traces).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from . import codec, encoder, hessian, tables
+
+
+@dataclass
+class ExpertSource:
+    """Source weights and routed calibration rows of one expert (device tensors)."""
+
+    w1: torch.Tensor          # gate  [intermediate, hidden]
+    w3: torch.Tensor          # up    [intermediate, hidden]
+    w2: torch.Tensor          # down  [hidden, intermediate]
+    rows: torch.Tensor        # routed inputs [R, hidden]
+    gates: torch.Tensor       # routing weights [R]
+    expert_id: int = 0
+
+
+@dataclass
+class MatrixPayload:
+    trellis: torch.Tensor     # int16 [in/16, out/16, 16*bits]
+    suh: torch.Tensor         # float16 [in]
+    svh: torch.Tensor         # float16 [out]
+    bits: int
+    proxy: float
+    g_scale: float
+
+
+@dataclass
+class ExpertPayload:
+    expert_id: int
+    bits: int
+    w1: MatrixPayload
+    w3: MatrixPayload
+    w2: MatrixPayload
+    routed_sse: float = float("nan")
+    routed_energy: float = float("nan")
+    payload_bytes: int = 0
+    evidence: dict = field(default_factory=dict)
+
+
+def situ(gate: torch.Tensor, up: torch.Tensor, *, beta: float = 4.0, linear_beta: float = 25.0) -> torch.Tensor:
+    """Kimi's bounded gated activation (qsrt/tp_simulator.py:82-93)."""
+
+    gate_value = beta * torch.tanh(gate.float() / beta) * torch.sigmoid(gate.float())
+    up_value = linear_beta * torch.tanh(up.float() / linear_beta)
+    return (gate_value * up_value).to(gate.dtype)
+
+
+def gated_middle(rows: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    gate = rows @ w1.T
+    up = rows @ w3.T
+    if activation == "silu":
+        return torch.nn.functional.silu(gate) * up
+    if activation == "situ":
+        return situ(gate, up)
+    raise ValueError(f"unknown activation {activation!r}")
+
+
+def quant_args_for(bits: int, device: torch.device, *, seed: int, sv_seed: int, sigma_reg: float = encoder.SIGMA_REG,
+                   tailbite_context: int = 128, codebook: str = tables.SQG_XOR_CHEB_T12, **extra) -> dict:
+    """The ``quant_args`` dictionary of a uniform-rate encode (qsrt/qsrt_codec_pilot.py:421-452)."""
+
+    args = {
+        "K": int(bits),
+        "seed": int(seed),
+        "sv_seed": int(sv_seed),
+        "sigma_reg": float(sigma_reg),
+        "devices": [str(device)],
+        "device_ratios": None,
+        "apply_out_scales": False,
+        "ldlq_tf32": False,
+        "tailbite_context": int(tailbite_context),
+        "sqg_e4m3_lut": tables.sqg_codebook_bytes(bits, codebook),
+    }
+    args.update(extra)
+    return args
+
+
+def _payload(result, args) -> MatrixPayload:
+    proxy, tensors = result
+    return MatrixPayload(tensors["trellis"], tensors["suh"], tensors["svh"], int(args["K"]), float(proxy), float(args["g_scale"]))
+
+
+def decode_matrix(payload: MatrixPayload, lut: torch.Tensor | None = None) -> torch.Tensor:
+    """Packed payload -> source-orientation ``[out, in]`` float32 weight."""
+
+    lut = tables.sqg_xor_cheb_t12_bytes(payload.bits) if lut is None else lut
+    states = codec.unpack_trellis_states(payload.trellis, payload.bits)
+    return codec.decode_exl3_weight(states, payload.suh, payload.svh, lut=lut).T.contiguous()
+
+
+def verify_payload_roundtrip(payload: MatrixPayload) -> bool:
+    """Pack -> decode-to-E4M3 closure: the decoded bytes must equal LUT[states] of a second,
+    independent unpack, and the states must close cyclically (bit-exact check on device)."""
+
+    lut = tables.sqg_xor_cheb_t12_bytes(payload.bits).to(payload.trellis.device)
+    raw = codec.decode_e4m3(payload.trellis, payload.bits, lut)
+    states = codec.unpack_trellis_states(payload.trellis, payload.bits)
+    expected = lut[(states.to(torch.int32) & 0xFFFF).long()]
+    repacked = codec.pack_trellis_edges(states, payload.bits)
+    return bool(torch.equal(raw, expected)) and bool(torch.equal(repacked, payload.trellis))
+
+
+def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch.device, layer_seed: int = 0,
+                        sigma_reg: float = encoder.SIGMA_REG, tailbite_context: int = 128,
+                        activation: str = "silu", down_from_reconstruction: bool = False,
+                        score: bool = True, h2_max_local_alpha: float = 0.75) -> list[ExpertPayload]:
+    """Encode a batch of experts at one uniform rate; see the module docstring for the flow."""
+
+    if not experts:
+        return []
+    device = torch.device(device)
+    results: list[ExpertPayload] = []
+    gate_up = []
+    weights_sq = []
+    middles = []
+    for ex in experts:
+        w = ex.gates.float().square()
+        weights_sq.append(w)
+        h13, _ = hessian.weighted_covariance(ex.rows, w, device=device, return_cpu=False)
+        shared = encoder.make_shared_h(ex.w1.shape[1], device, h13)
+        del h13
+        seed = 2 * (layer_seed * 100003 + ex.expert_id) * 3
+        args1 = quant_args_for(bits, device, seed=seed, sv_seed=seed + 1, sigma_reg=sigma_reg, tailbite_context=tailbite_context)
+        args3 = quant_args_for(bits, device, seed=seed, sv_seed=seed + 2, sigma_reg=sigma_reg, tailbite_context=tailbite_context)
+        out = encoder.quantize_uniform_batch(
+            [ex.w1.T.float().contiguous(), ex.w3.T.float().contiguous()], [shared, shared], [args1, args3]
+        )
+        p1, p3 = _payload(out[0], args1), _payload(out[1], args3)
+        gate_up.append((p1, p3))
+        if down_from_reconstruction:
+            middle = gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
+        else:
+            middle = gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation)
+        middles.append(middle)
+
+    down_weights, down_h, down_args, evidence = [], [], [], []
+    for ex, w, middle in zip(experts, weights_sq, middles):
+        local_h2, _ = hessian.weighted_covariance(middle, w, device=device, return_cpu=False)
+        h2, info = hessian.adaptive_identity_shrinkage(local_h2, w, max_local_alpha=h2_max_local_alpha)
+        del local_h2
+        down_h.append(encoder.make_shared_h(ex.w2.shape[1], device, h2))
+        del h2
+        seed = 2 * (layer_seed * 100003 + ex.expert_id) * 3 + 3
+        down_args.append(quant_args_for(bits, device, seed=seed, sv_seed=seed + 1, sigma_reg=sigma_reg,
+                                        tailbite_context=tailbite_context))
+        down_weights.append(ex.w2.T.float().contiguous())
+        evidence.append(info)
+    down_out = encoder.quantize_uniform_batch(down_weights, down_h, down_args)
+
+    for ex, (p1, p3), res, args, w, middle, info in zip(experts, gate_up, down_out, down_args, weights_sq, middles, evidence):
+        p2 = _payload(res, args)
+        payload = ExpertPayload(ex.expert_id, bits, p1, p3, p2, evidence=info)
+        payload.payload_bytes = sum(p.trellis.numel() * 2 + p.suh.numel() * 2 + p.svh.numel() * 2 for p in (p1, p3, p2))
+        if score:
+            teacher = middle @ ex.w2.float().T
+            decoded_mid = gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
+            student = decoded_mid @ decode_matrix(p2).T
+            payload.routed_sse = float(((student - teacher).double().square().sum(dim=1) * w.double()).sum())
+            payload.routed_energy = float((teacher.double().square().sum(dim=1) * w.double()).sum())
+        results.append(payload)
+    return results

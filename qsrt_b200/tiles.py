@@ -26,6 +26,32 @@ _UNSUPPORTED_KEYS = {
 
 # (device, bits, source key) -> (source tensor, state-indexed device table, predecessor-major
 # device table, max |label|)
+# When a list, every tile-search launch appends (start_event, end_event, n_tiles, bits); the
+# benchmark uses it to time the dominant kernel on the launching stream.
+search_timings: list | None = None
+
+
+class timed_search:
+    """Context manager recording CUDA events around one tile-search launch."""
+
+    def __init__(self, device: torch.device, n_tiles: int, bits: int) -> None:
+        self.active = search_timings is not None
+        self.device, self.n_tiles, self.bits = device, n_tiles, bits
+
+    def __enter__(self):
+        if self.active:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        if self.active:
+            self.end.record(torch.cuda.current_stream(self.device))
+            search_timings.append((self.start, self.end, self.n_tiles, self.bits))
+        return False
+
+
 _tables: dict[tuple[str, int, int], tuple[torch.Tensor, torch.Tensor, torch.Tensor, float]] = {}
 _scratch: dict[tuple[str, int], torch.Tensor] = {}
 
@@ -109,7 +135,7 @@ def encode_tiles(
     if tiles.shape[0] == 0:
         return output, indices
     scratch = traceback_scratch(device, bits)
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), timed_search(device, tiles.shape[0], bits):
         _lib.check(
             _lib.lib().qsrtb_quantize_tiles(
                 tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits,
