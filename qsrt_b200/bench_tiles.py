@@ -40,8 +40,10 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--seed", type=int, default=20260816)
+    p.add_argument("--units", type=int, default=2, help="work units per thread of the search kernel (1 or 2)")
     args = p.parse_args()
     device = torch.device("cuda:0")
+    tile_api.set_units_per_thread(args.units)
     x = make_tiles(args.family, args.tiles, args.seed).to(device)
     lut = tables.sqg_xor_cheb_t12_bytes(args.bits)
     for _ in range(args.warmup):
@@ -58,7 +60,7 @@ def main() -> None:
     ms = sorted(times)[len(times) // 2]
     metrics = args.tiles * (256 + 2 * args.context) * METRICS_PER_STEP
     print(json.dumps({
-        "tiles": args.tiles, "bits": args.bits, "context": args.context, "family": args.family,
+        "tiles": args.tiles, "bits": args.bits, "context": args.context, "family": args.family, "units": args.units,
         "median_ms": ms, "ktiles_per_s": args.tiles / ms, "mweights_per_s": args.tiles * 256 / ms / 1e3,
         "g_branch_metrics_per_s": metrics / ms / 1e6,
     }))

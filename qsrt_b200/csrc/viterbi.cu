@@ -35,7 +35,7 @@
 
 namespace {
 
-constexpr int kThreads = 1024;
+constexpr int kUnits = 1024;  // work units per tile; a thread owns UNITS of them
 constexpr uint32_t kInf2 = 0x7c007c00u;
 constexpr uint32_t kMax2 = 0x7bff7bffu;
 constexpr int kSafeSteps = 8;  // >= ceil((16-K)/K) for K in {2,3,4}: all states reachable after
@@ -47,13 +47,12 @@ struct Geo {
     static constexpr int Kr = 16 - K;
     static constexpr int edges = 1 << Kr;
     static constexpr int NK = 1 << K;                  // predecessors per out-edge
-    static constexpr int E = edges / kThreads;         // out-edges per thread: 16 / 8 / 4
-    static constexpr int P = E / 2;                    // out-edge pairs per thread
-    static constexpr int Q = (E >> K) > 0 ? (E >> K) : 1;  // predecessor groups per thread
+    static constexpr int E = edges / kUnits;           // out-edges per unit: 16 / 8 / 4
+    static constexpr int P = E / 2;                    // out-edge pairs per unit
+    static constexpr int Q = (E >> K) > 0 ? (E >> K) : 1;  // predecessor groups per unit
     static constexpr int pred_stride = 1 << (Kr - K);  // 4096 / 1024 / 256
     static constexpr int row_bytes = (K == 2) ? edges / 4 : edges / 2;  // 4096 / 4096 / 2048
     static constexpr int rows_per_batch = (2 * edges * 2) / row_bytes;  // 16 / 8 / 8
-    static constexpr int dec_bytes = row_bytes / kThreads;              // 4 / 4 / 2
     static constexpr int JB = Kr - 10;                 // bits of the per-thread scan index
 };
 
@@ -104,14 +103,16 @@ __device__ __forceinline__ MinIdx tournament(const __half2 (&c)[NK])
 //   L        : the thread's 64 label bytes, [pair][pred/2] words of two fp8x2
 //   inc/cur  : previous / new path costs (shared memory)
 //   track    : MODE_FAST running max of stored costs; MODE_K2 running min of this step
-template <int K, int MODE, bool FIRST, bool CONSTRAINED, bool RECORD>
-__device__ __forceinline__ void acs_step(const uint32_t (&L)[16], const __half* inc, __half* cur,
-                                         __half w, int pre_state, __half2 shift2,
+//   u        : the unit (0..1023) these labels belong to
+// NL = 16: labels kept as packed fp8 pairs and converted every step; NL = 32: labels kept as
+// half2 (one register per out-edge pair and predecessor), no conversion in the loop.
+template <int K, int MODE, bool FIRST, bool CONSTRAINED, bool RECORD, int NL>
+__device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, const __half* inc,
+                                         __half* cur, __half w, int pre_state, __half2 shift2,
                                          uint8_t* dec_row, __half2& track)
 {
     using G = Geo<K>;
     constexpr int NK = G::NK;
-    const int u = threadIdx.x;
     const int qbase = (G::E * u) >> K;
     const __half2 w2 = __half2half2(w);
     const __half2 inf2 = u2h2(kInf2);
@@ -140,8 +141,13 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[16], const __half* 
         __half2 c[NK];
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
-            const uint32_t word = L[j * (NK / 2) + (k >> 1)];
-            const __half2 d = fp8x2_to_half2((k & 1) ? (word >> 16) : (word & 0xffffu));
+            __half2 d;
+            if constexpr (NL == 32) {
+                d = u2h2(L[j * NK + k]);
+            } else {
+                const uint32_t word = L[j * (NK / 2) + (k >> 1)];
+                d = fp8x2_to_half2((k & 1) ? (word >> 16) : (word & 0xffffu));
+            }
             const __half2 dh = __hsub2(d, w2);
             if constexpr (FIRST) {
                 __half2 v = __hmul2(dh, dh);
@@ -228,30 +234,36 @@ __device__ __forceinline__ uint32_t half_key(uint32_t h)
 //   streams (cuh:388-423); otherwise 1024 threads hold one stream (cuh:365-387, k2 cuh:276-325).
 // In both, shuffle trees that only replace on strict less-than prefer the partner whose
 // lane / slot index is smaller after 5-bit reversal, and a thread keeps its earliest edge.
-template <int K, bool TREE512>
+// The key of an edge depends only on the edge, so the reduction may be carried out by any
+// number of threads in any order: each thread folds the edges of UNITS reference threads.
+template <int K, bool TREE512, int UNITS>
 __device__ __forceinline__ int boundary_argmin(const __half* costs, uint32_t* red)
 {
     using G = Geo<K>;
-    const int t = threadIdx.x;
-    const uint32_t lane = t & 31, warp = t >> 5;
-    uint32_t prio_hi;
-    if constexpr (TREE512) {
-        const uint32_t slot = ((t >> 9) & 1) * 16 + ((t >> 5) & 15);
-        prio_hi = (bitrev5(slot) << 5) | bitrev5(lane);
-    } else {
-        prio_hi = (bitrev5(warp) << 5) | bitrev5(lane);
-    }
+    constexpr int THREADS = kUnits / UNITS;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t best = 0xffffffffu;
 #pragma unroll
-    for (int j = 0; j < (1 << G::JB); ++j) {
-        const uint32_t h = *reinterpret_cast<const uint16_t*>(costs + t + 1024 * j);
-        const uint32_t key = (half_key(h) << 16) | (prio_hi << G::JB) | uint32_t(j);
-        best = min(best, key);
+    for (int uu = 0; uu < UNITS; ++uu) {
+        const int t = threadIdx.x + uu * THREADS;  // thread index in the reference's 1024-thread block
+        uint32_t prio_hi;
+        if constexpr (TREE512) {
+            const uint32_t slot = ((t >> 9) & 1) * 16 + ((t >> 5) & 15);
+            prio_hi = (bitrev5(slot) << 5) | bitrev5(t & 31);
+        } else {
+            prio_hi = (bitrev5(t >> 5) << 5) | bitrev5(t & 31);
+        }
+#pragma unroll
+        for (int j = 0; j < (1 << G::JB); ++j) {
+            const uint32_t h = *reinterpret_cast<const uint16_t*>(costs + t + 1024 * j);
+            const uint32_t key = (half_key(h) << 16) | (prio_hi << G::JB) | uint32_t(j);
+            best = min(best, key);
+        }
     }
     best = __reduce_min_sync(0xffffffffu, best);
     if (lane == 0) red[warp] = best;
     __syncthreads();
-    uint32_t v = red[lane];
+    uint32_t v = lane < THREADS / 32 ? red[lane] : 0xffffffffu;
     v = __reduce_min_sync(0xffffffffu, v);
     __syncthreads();
     const uint32_t j = v & ((1u << G::JB) - 1);
@@ -265,7 +277,7 @@ __device__ __forceinline__ int boundary_argmin(const __half* costs, uint32_t* re
 
 // Walk survivor rows ri_hi .. 0 starting from `edge`; returns the state before row 0.
 // Rows are streamed from the CTA's scratch slice through `rowbuf` (the idle cost buffers).
-template <int K>
+template <int K, int UNITS>
 __device__ __forceinline__ int traceback(uint8_t* scratch, uint8_t* rowbuf, int ri_hi, int edge,
                                          bool write, uint16_t* sh_states, int* sh_edge)
 {
@@ -275,7 +287,7 @@ __device__ __forceinline__ int traceback(uint8_t* scratch, uint8_t* rowbuf, int 
         const int nvec = (hi - lo + 1) * (G::row_bytes / 16);
         const uint4* src = reinterpret_cast<const uint4*>(scratch + size_t(lo) * G::row_bytes);
         uint4* dst = reinterpret_cast<uint4*>(rowbuf);
-        for (int v = threadIdx.x; v < nvec; v += kThreads) dst[v] = src[v];
+        for (int v = threadIdx.x; v < nvec; v += kUnits / UNITS) dst[v] = src[v];
         __syncthreads();
         if (threadIdx.x == 0) {
             for (int ri = hi; ri >= lo; --ri) {
@@ -309,11 +321,13 @@ struct Smem {
 
 // Encode the tile whose rounded input is already in sm->in_h.  Returns (block-uniform) whether
 // the result is valid; only MODE_FAST can return false.
-template <int K, int MODE>
-__device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, __half* cost0,
+template <int K, int MODE, int UNITS, int NL>
+__device__ __forceinline__ bool encode_tile(const uint32_t (&L)[UNITS][NL], Smem* sm, __half* cost0,
                                             __half* cost1, uint8_t* scratch, int context)
 {
     using G = Geo<K>;
+    constexpr int THREADS = kUnits / UNITS;
+    constexpr int WARPS = THREADS / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __half* cur = cost0;
     __half* inc = cost1;
@@ -324,7 +338,7 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
     // the shift used by step s is the block minimum stored by step s-2 when that is >= 1024.
     auto k2_fold = [&](int s) {
         if (warp == 0) {
-            __half m = sm->warp_mins[(s - 1) & 1][lane];
+            __half m = lane < WARPS ? sm->warp_mins[(s - 1) & 1][lane] : __ushort_as_half(0x7c00);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = __hmin(m, __shfl_down_sync(0xffffffffu, m, o));
             if (lane == 0)
@@ -337,6 +351,11 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
         for (int o = 16; o > 0; o >>= 1) m = __hmin(m, __shfl_down_sync(0xffffffffu, m, o));
         if (lane == 0) sm->warp_mins[s & 1][warp] = m;
     };
+
+#define UNIT_LOOP(...)                                                        \
+    do {                                                                      \
+        _Pragma("unroll") for (int uu = 0; uu < UNITS; ++uu) { __VA_ARGS__; } \
+    } while (0)
 
     auto run_pass = [&](int roll, int steps, int pre_state, int trace_start, auto constrained_tag) {
         constexpr bool CONSTRAINED = decltype(constrained_tag)::value;
@@ -360,27 +379,27 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
             }
             if (i == 0) {
                 if constexpr (MODE == MODE_K2)
-                    acs_step<K, MODE, true, CONSTRAINED, CONSTRAINED>(L, inc, cur, w, pre_state, shift2, dec_row, step_min2);
+                    UNIT_LOOP(acs_step<K, MODE, true, CONSTRAINED, CONSTRAINED, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, pre_state, shift2, dec_row, step_min2));
                 else if constexpr (MODE == MODE_FAST && CONSTRAINED)
-                    acs_step<K, MODE_SAFE, true, true, true>(L, inc, cur, w, pre_state, shift2, dec_row, track_max);
+                    UNIT_LOOP(acs_step<K, MODE_SAFE, true, true, true, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, pre_state, shift2, dec_row, track_max));
                 else
-                    acs_step<K, MODE, true, CONSTRAINED, CONSTRAINED>(L, inc, cur, w, pre_state, shift2, dec_row, track_max);
+                    UNIT_LOOP(acs_step<K, MODE, true, CONSTRAINED, CONSTRAINED, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, pre_state, shift2, dec_row, track_max));
             } else if (i < trace_start) {
                 if constexpr (MODE == MODE_K2)
-                    acs_step<K, MODE, false, false, false>(L, inc, cur, w, -1, shift2, dec_row, step_min2);
+                    UNIT_LOOP(acs_step<K, MODE, false, false, false, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, step_min2));
                 else
-                    acs_step<K, MODE, false, false, false>(L, inc, cur, w, -1, shift2, dec_row, track_max);
+                    UNIT_LOOP(acs_step<K, MODE, false, false, false, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, track_max));
             } else {
                 if constexpr (MODE == MODE_K2) {
-                    acs_step<K, MODE, false, false, true>(L, inc, cur, w, -1, shift2, dec_row, step_min2);
+                    UNIT_LOOP(acs_step<K, MODE, false, false, true, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, step_min2));
                 } else if constexpr (MODE == MODE_FAST && CONSTRAINED) {
                     // Unreachable states exist for the first few constrained steps.
                     if (i < kSafeSteps)
-                        acs_step<K, MODE_SAFE, false, false, true>(L, inc, cur, w, -1, shift2, dec_row, track_max);
+                        UNIT_LOOP(acs_step<K, MODE_SAFE, false, false, true, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, track_max));
                     else
-                        acs_step<K, MODE, false, false, true>(L, inc, cur, w, -1, shift2, dec_row, track_max);
+                        UNIT_LOOP(acs_step<K, MODE, false, false, true, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, track_max));
                 } else {
-                    acs_step<K, MODE, false, false, true>(L, inc, cur, w, -1, shift2, dec_row, track_max);
+                    UNIT_LOOP(acs_step<K, MODE, false, false, true, NL>(L[uu], int(threadIdx.x) + uu * THREADS, inc, cur, w, -1, shift2, dec_row, track_max));
                 }
             }
             if constexpr (MODE == MODE_K2) k2_publish(i, step_min2);
@@ -397,10 +416,10 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
     }
     int boundary;
     if constexpr (MODE == MODE_K2)
-        boundary = boundary_argmin<K, false>(cur, sm->red);  // final primer step (k2 cuh:282)
+        boundary = boundary_argmin<K, false, UNITS>(cur, sm->red);  // final primer step (k2 cuh:282)
     else
-        boundary = boundary_argmin<K, K != 2>(inc, sm->red);  // step before the last (cuh:375,401)
-    const int end_state = traceback<K>(scratch, reinterpret_cast<uint8_t*>(cost0), context - 1,
+        boundary = boundary_argmin<K, K != 2, UNITS>(inc, sm->red);  // step before the last (cuh:375,401)
+    const int end_state = traceback<K, UNITS>(scratch, reinterpret_cast<uint8_t*>(cost0), context - 1,
                                        boundary, false, sm->states, &sm->edge);
 
     // Constrained pass: starts from and must return to end_state.
@@ -411,9 +430,10 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[16], Smem* sm, _
         if (__syncthreads_or(over)) valid = false;
     }
     if (valid)
-        traceback<K>(scratch, reinterpret_cast<uint8_t*>(cost0), 255, end_state, true, sm->states,
+        traceback<K, UNITS>(scratch, reinterpret_cast<uint8_t*>(cost0), 255, end_state, true, sm->states,
                      &sm->edge);
     return valid;
+#undef UNIT_LOOP
 }
 
 // Where a CTA finds tile `t` and where its results go.
@@ -452,8 +472,8 @@ __device__ __forceinline__ int tensor_core_rc(int t, int& col)
     return row;
 }
 
-template <int K, bool DEDICATED>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int K, bool DEDICATED, int UNITS>
+__global__ void __launch_bounds__(kUnits / UNITS, 1)
 viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
                const uint8_t* __restrict__ lut_state, uint8_t* scratch_base, int64_t n_tiles,
                int context)
@@ -465,13 +485,27 @@ viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
     Smem* sm = reinterpret_cast<Smem*>(smem_raw + 2 * G::edges * sizeof(__half));
     uint8_t* scratch = scratch_base + size_t(blockIdx.x) * 256 * G::row_bytes;
 
-    uint32_t L[16];
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(lut_pm) + 4 * threadIdx.x;
+    // With two units per thread there is room to keep the labels as half2 (32 registers per
+    // unit), which takes the fp8 -> half conversion out of the add-compare-select loop.
+    constexpr int THREADS = kUnits / UNITS;
+    constexpr int NL = UNITS >= 2 ? 32 : 16;
+    uint32_t L[UNITS][NL];
+#pragma unroll
+    for (int uu = 0; uu < UNITS; ++uu) {
+        const uint4* src = reinterpret_cast<const uint4*>(lut_pm) + 4 * (threadIdx.x + uu * THREADS);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint4 v = src[i];
-            L[4 * i + 0] = v.x; L[4 * i + 1] = v.y; L[4 * i + 2] = v.z; L[4 * i + 3] = v.w;
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if constexpr (NL == 32) {
+                    L[uu][2 * (4 * i + q) + 0] = h22u(fp8x2_to_half2(words[q] & 0xffffu));
+                    L[uu][2 * (4 * i + q) + 1] = h22u(fp8x2_to_half2(words[q] >> 16));
+                } else {
+                    L[uu][4 * i + q] = words[q];
+                }
+            }
         }
     }
 
@@ -506,10 +540,10 @@ viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
         }
         __syncthreads();
         if constexpr (DEDICATED) {
-            encode_tile<K, MODE_K2>(L, sm, cost0, cost1, scratch, context);
+            encode_tile<K, MODE_K2, UNITS, NL>(L, sm, cost0, cost1, scratch, context);
         } else {
-            if (!encode_tile<K, MODE_FAST>(L, sm, cost0, cost1, scratch, context))
-                encode_tile<K, MODE_SAFE>(L, sm, cost0, cost1, scratch, context);
+            if (!encode_tile<K, MODE_FAST, UNITS, NL>(L, sm, cost0, cost1, scratch, context))
+                encode_tile<K, MODE_SAFE, UNITS, NL>(L, sm, cost0, cost1, scratch, context);
         }
         if (threadIdx.x < 256) {
             const uint16_t s = sm->states[threadIdx.x];
@@ -540,7 +574,7 @@ int resident_ctas()
     return sms;
 }
 
-template <int K, bool DEDICATED>
+template <int K, bool DEDICATED, int UNITS>
 int launch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
            int context, void* scratch, size_t scratch_bytes, cudaStream_t stream)
 {
@@ -551,11 +585,11 @@ int launch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const ui
     const size_t slice = size_t(256) * G::row_bytes;
     if (scratch_bytes < slice) return qsrtb_fail(QSRTB_ESCRATCH, "traceback scratch smaller than one slice");
     if (int64_t(scratch_bytes / slice) < grid) grid = int64_t(scratch_bytes / slice);
-    auto kernel = viterbi_kernel<K, DEDICATED>;
+    auto kernel = viterbi_kernel<K, DEDICATED, UNITS>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            int(smem_bytes<K>()));
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaFuncSetAttribute(viterbi)");
-    kernel<<<dim3(unsigned(grid)), dim3(kThreads), smem_bytes<K>(), stream>>>(
+    kernel<<<dim3(unsigned(grid)), dim3(kUnits / UNITS), smem_bytes<K>(), stream>>>(
         io, lut_pm, lut_state, static_cast<uint8_t*>(scratch), n_tiles, context);
     err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "viterbi kernel launch");
@@ -623,19 +657,32 @@ int check_common(int bits, int tailbite_context, int variant, int64_t n_tiles)
     return QSRTB_OK;
 }
 
-int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
-             int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
+// Units per thread of the add-compare-select loop: 2 = 512 threads with half2 labels in
+// registers, 1 = 1024 threads with packed fp8 labels.  Same results either way.
+int g_units = 2;
+
+template <int UNITS>
+int dispatch_units(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
+                   int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
 {
     switch (bits) {
         case 2:
             if (variant == 1)
-                return launch<2, true>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
-            return launch<2, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
+                return launch<2, true, UNITS>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
+            return launch<2, false, UNITS>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
         case 3:
-            return launch<3, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
+            return launch<3, false, UNITS>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
         default:
-            return launch<4, false>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
+            return launch<4, false, UNITS>(io, n_tiles, lut_state, lut_pm, context, scratch, scratch_bytes, s);
     }
+}
+
+int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
+             int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
+{
+    if (g_units == 1)
+        return dispatch_units<1>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
+    return dispatch_units<2>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
 }
 
 }  // namespace
@@ -699,4 +746,12 @@ extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float
     io.rows_mode = 1;
     return dispatch(io, n_tiles, lut_state, lut_pm, bits, tailbite_context, variant, scratch,
                     scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// Tuning knob (not part of the reference interface): units per thread, 1 or 2.
+extern "C" int qsrtb_viterbi_set_units(int units)
+{
+    if (units != 1 && units != 2) return qsrtb_fail(QSRTB_EINVAL, "units per thread must be 1 or 2");
+    g_units = units;
+    return QSRTB_OK;
 }

@@ -60,6 +60,13 @@ def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def set_units_per_thread(units: int) -> None:
+    """Tuning knob of the search kernel: 2 (512 threads, half2 labels in registers, default)
+    or 1 (1024 threads, packed fp8 labels).  Results do not depend on it."""
+
+    _lib.check(_lib.lib().qsrtb_viterbi_set_units(int(units)), "qsrtb_viterbi_set_units")
+
+
 def prepared_table(codebook: torch.Tensor, bits: int, device: torch.device):
     """Device copies of a state-indexed table: (state order, predecessor-major order, amax)."""
 

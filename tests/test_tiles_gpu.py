@@ -99,6 +99,27 @@ def test_saturated_cost_paths_stay_closed(cuda_device, bits):
     assert oracle.states_close(states.cpu().numpy(), bits)
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_thread_layouts_agree(cuda_device, bits):
+    """1024 threads with fp8 labels and 512 threads with half2 labels give the same bits."""
+
+    tiles = helpers.mixed_tiles(5, seed=31 + bits).to(cuda_device)
+    lut = _lut(bits)
+    try:
+        tile_api.set_units_per_thread(1)
+        out1, idx1 = tile_api.encode_tiles(tiles, lut, bits, 128)
+        gen1 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True)
+        tile_api.set_units_per_thread(2)
+        out2, idx2 = tile_api.encode_tiles(tiles, lut, bits, 128)
+        gen2 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True)
+    finally:
+        tile_api.set_units_per_thread(2)
+    assert torch.equal(idx1, idx2) and torch.equal(out1, out2)
+    assert torch.equal(gen1[1], gen2[1])
+    ref_out, ref_idx = oracle.quantize_tiles(tiles.cpu().numpy()[:8], lut.numpy(), bits, 128)
+    assert np.array_equal(idx2.cpu().numpy()[:8], ref_idx)
+
+
 def test_empty_and_ragged_batches(cuda_device):
     lut = _lut(3)
     out, idx = tile_api.encode_tiles(torch.empty((0, 256), device=cuda_device), lut, 3)
