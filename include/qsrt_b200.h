@@ -59,8 +59,8 @@ int qsrtb_lut_prepare(const uint8_t* lut_state, int bits, uint8_t* lut_pm, float
 int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 
 /* Tuning knob without a reference counterpart: work units per thread of the search kernel
- * (2 = 512 threads holding half2 labels in registers [default], 1 = 1024 threads holding fp8
- * labels).  Process-wide; results are identical. */
+ * (2 = 512 threads holding half2 labels in registers, 1 = 1024 threads holding fp8 labels,
+ * 0 = per-rate default).  Process-wide; results are identical. */
 int qsrtb_viterbi_set_units(int units);
 
 int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-core order   */

@@ -40,7 +40,7 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--seed", type=int, default=20260816)
-    p.add_argument("--units", type=int, default=2, help="work units per thread of the search kernel (1 or 2)")
+    p.add_argument("--units", type=int, default=0, help="work units per thread of the search kernel (0 auto, 1 or 2)")
     args = p.parse_args()
     device = torch.device("cuda:0")
     tile_api.set_units_per_thread(args.units)

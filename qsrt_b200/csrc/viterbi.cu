@@ -658,8 +658,9 @@ int check_common(int bits, int tailbite_context, int variant, int64_t n_tiles)
 }
 
 // Units per thread of the add-compare-select loop: 2 = 512 threads with half2 labels in
-// registers, 1 = 1024 threads with packed fp8 labels.  Same results either way.
-int g_units = 2;
+// registers, 1 = 1024 threads with packed fp8 labels, 0 = the faster of the two as measured
+// on B200 (K2 and K4: 2, K3: 1).  Same results either way.
+int g_units = 0;
 
 template <int UNITS>
 int dispatch_units(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
@@ -680,7 +681,8 @@ int dispatch_units(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, 
 int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
              int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
 {
-    if (g_units == 1)
+    const int units = g_units != 0 ? g_units : (bits == 3 ? 1 : 2);
+    if (units == 1)
         return dispatch_units<1>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
     return dispatch_units<2>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
 }
@@ -751,7 +753,7 @@ extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float
 // Tuning knob (not part of the reference interface): units per thread, 1 or 2.
 extern "C" int qsrtb_viterbi_set_units(int units)
 {
-    if (units != 1 && units != 2) return qsrtb_fail(QSRTB_EINVAL, "units per thread must be 1 or 2");
+    if (units < 0 || units > 2) return qsrtb_fail(QSRTB_EINVAL, "units per thread must be 0 (auto), 1 or 2");
     g_units = units;
     return QSRTB_OK;
 }

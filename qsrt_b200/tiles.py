@@ -61,8 +61,8 @@ def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
 
 
 def set_units_per_thread(units: int) -> None:
-    """Tuning knob of the search kernel: 2 (512 threads, half2 labels in registers, default)
-    or 1 (1024 threads, packed fp8 labels).  Results do not depend on it."""
+    """Tuning knob of the search kernel: 2 (512 threads, half2 labels in registers),
+    1 (1024 threads, packed fp8 labels) or 0 (per-rate default).  Results do not depend on it."""
 
     _lib.check(_lib.lib().qsrtb_viterbi_set_units(int(units)), "qsrtb_viterbi_set_units")
 

@@ -1,0 +1,126 @@
+"""GPU parity of Hessian accumulation (H1) and the expert pipeline (C1, P1/D1 closure)."""
+
+import numpy as np
+import pytest
+import torch
+
+from qsrt_b200 import codec, hessian, pipeline, tables
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_fro(a, b):
+    a, b = a.double(), b.double()
+    return float(torch.linalg.vector_norm(a - b) / torch.linalg.vector_norm(b))
+
+
+@pytest.mark.parametrize("rows,dim", [(1365, 512), (4096, 1024), (77, 192), (1, 64)])
+def test_weighted_covariance_within_1e5_of_fp64(cuda_device, rows, dim):
+    """Hessians must be within 1e-5 relative Frobenius error (tolerance of the path's spec)."""
+
+    g = torch.Generator().manual_seed(rows + dim)
+    x = torch.randn((rows, dim), generator=g) * torch.exp(0.5 * torch.randn(dim, generator=g))
+    w = torch.rand(rows, generator=g).square()
+    got, denom = hessian.weighted_covariance(x, w, device=cuda_device)
+    x64 = x.double()
+    ref = (x64.T * w.double()) @ x64 / w.double().sum()
+    assert abs(denom - float(w.double().sum())) < 1e-9 * denom
+    assert _rel_fro(got, ref) < 1e-5
+    assert torch.equal(got, got.T)
+    # the reference's own float32 formulation (qsrt/candidate_hessian.py:96-108) on CPU
+    acc = torch.zeros((dim, dim))
+    for begin in range(0, rows, 256):
+        v = x[begin:begin + 256]
+        acc.addmm_(v.T, v * w[begin:begin + 256, None])
+    acc = acc.div_(denom)
+    acc = (acc + acc.T) * 0.5
+    assert _rel_fro(got, acc) < 1e-5
+
+
+def test_covariance_chunked_accumulation_and_errors(cuda_device):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((1000, 256), generator=g)
+    w = torch.rand(1000, generator=g)
+    one, _ = hessian.weighted_covariance(x, w, device=cuda_device)
+    many, _ = hessian.weighted_covariance(x, w, device=cuda_device, chunk_rows=300)
+    assert _rel_fro(many, one) < 1e-6
+    with pytest.raises(ValueError):
+        hessian.weighted_covariance(x, w[:-1], device=cuda_device)
+    with pytest.raises(ValueError):
+        hessian.weighted_covariance(x, -w, device=cuda_device)
+    with pytest.raises(ValueError):
+        hessian.weighted_covariance(x, torch.zeros(1000), device=cuda_device)
+    with pytest.raises(ValueError):
+        hessian.weighted_covariance(x[:0], w[:0], device=cuda_device)
+    bad = x.clone()
+    bad[3, 3] = float("nan")
+    with pytest.raises(ValueError):
+        hessian.weighted_covariance(bad, w, device=cuda_device)
+
+
+def test_oas_shrinkage_matches_reference_formula(cuda_device):
+    """adaptive_identity_shrinkage restated from qsrt/candidate_hessian.py:156-216."""
+
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((200, 64), generator=g)
+    w = torch.rand(200, generator=g)
+    local, _ = hessian.weighted_covariance(x, w, device=cuda_device, return_cpu=False)
+    blended, info = hessian.adaptive_identity_shrinkage(local, w)
+    n_eff = float(w.double().sum() ** 2 / w.double().square().sum())
+    l64 = local.double().cpu()
+    mu = torch.trace(l64) / 64
+    ms = l64.square().mean()
+    rho = min(1.0, max(0.0, float((ms + mu ** 2) / ((n_eff + 1.0) * (ms - mu ** 2 / 64)))))
+    alpha = min(0.75, 1.0 - rho)
+    assert abs(info["oas_shrinkage"] - rho) < 1e-12 and abs(info["local_alpha"] - alpha) < 1e-12
+    expect = torch.lerp(torch.eye(64) * float(mu), local.cpu(), alpha)
+    assert _rel_fro(blended.cpu(), (expect + expect.T) * 0.5) < 1e-6
+
+
+def _tiny_experts(device, count=2, hidden=256, inter=128, tokens=600):
+    g = torch.Generator().manual_seed(123)
+    x = torch.randn((tokens, hidden), generator=g) * torch.exp(0.5 * torch.randn(hidden, generator=g))
+    out = []
+    for e in range(count):
+        w1 = torch.randn((inter, hidden), generator=g) * 0.02
+        w3 = 0.5 * w1 + (0.75 ** 0.5) * torch.randn((inter, hidden), generator=g) * 0.02
+        w2 = torch.randn((hidden, inter), generator=g) * 0.02
+        idx = torch.randperm(tokens, generator=g)[: 300 + 50 * e]
+        gates = torch.softmax(torch.randn((tokens, 8), generator=g), dim=-1)[idx, 0]
+        out.append(pipeline.ExpertSource(w1.to(device), w3.to(device), w2.to(device), x[idx].to(device),
+                                         gates.to(device), expert_id=e))
+    return out
+
+
+@pytest.mark.parametrize("bits", [2, 3])
+def test_expert_batch_payloads_close_and_score(cuda_device, bits):
+    experts = _tiny_experts(cuda_device)
+    payloads = pipeline.encode_expert_batch(experts, bits=bits, device=cuda_device, sigma_reg=1e-2)
+    assert len(payloads) == 2
+    for ex, p in zip(experts, payloads):
+        for name, mp, src in (("w1", p.w1, ex.w1), ("w3", p.w3, ex.w3), ("w2", p.w2, ex.w2)):
+            assert mp.trellis.shape == (src.shape[1] // 16, src.shape[0] // 16, 16 * bits)
+            assert pipeline.verify_payload_roundtrip(mp), name
+            decoded = pipeline.decode_matrix(mp)
+            rel = float(((decoded - src) ** 2).mean() / (src ** 2).mean())
+            assert rel < (0.35 if bits == 2 else 0.12), (name, rel)  # plain MSE; the encoder minimises the Hessian-weighted error
+            assert 0.0 < mp.proxy < 1.0
+        assert 0.0 < p.routed_sse < p.routed_energy
+        assert p.payload_bytes == sum(m.trellis.numel() * 2 + m.suh.numel() * 2 + m.svh.numel() * 2
+                                      for m in (p.w1, p.w3, p.w2))
+    # a higher rate must lower the routed error of the same expert
+    if bits == 2:
+        better = pipeline.encode_expert_batch(experts[:1], bits=4, device=cuda_device, sigma_reg=1e-2)
+        assert better[0].routed_sse < payloads[0].routed_sse
+
+
+def test_down_from_reconstruction_flow(cuda_device):
+    """Gate/up first, reconstructed activations form the down covariance (GLM-style flow)."""
+
+    experts = _tiny_experts(cuda_device, count=1)
+    a = pipeline.encode_expert_batch(experts, bits=2, device=cuda_device, sigma_reg=1e-2)[0]
+    b = pipeline.encode_expert_batch(experts, bits=2, device=cuda_device, sigma_reg=1e-2,
+                                     down_from_reconstruction=True)[0]
+    assert torch.equal(a.w1.trellis, b.w1.trellis)          # gate/up do not depend on the flag
+    assert not torch.equal(a.w2.trellis, b.w2.trellis)      # the down Hessian does
+    assert pipeline.verify_payload_roundtrip(b.w2)
