@@ -75,6 +75,20 @@ int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-cor
                          void* scratch, size_t scratch_bytes,
                          void* stream);
 
+/* Tile search for callers that cannot allocate device memory (no counterpart in the
+ * reference, which always allocates its traceback buffers with torch).  Same inputs, outputs
+ * and results as qsrtb_quantize_tiles, but the survivor scratch is a fixed 16 MiB array inside
+ * the library image on each GPU, so the call performs no allocation of any kind.
+ *   - at most 4096 tiles per call (QSRTB_EINVAL beyond that); the small scratch limits the
+ *     grid to 16 CTAs (K2, K3) or 32 (K4), so it is slower than the regular entry point;
+ *   - the first call on a device looks up the array's device address; make that first call
+ *     outside any stream capture;
+ *   - all calls share the array: calls that overlap in time on one GPU race, serialise them.
+ */
+int qsrtb_quantize_tiles_static(const float* tiles, int64_t n_tiles, const uint8_t* lut_state,
+                                const uint8_t* lut_pm, int bits, int tailbite_context,
+                                int variant, float* out_tiles, int16_t* out_states, void* stream);
+
 /* ---- H1: calibration Hessian accumulation ------------------------------------------------
  * Replaces the chunked `accumulator.addmm_(x.T, x * w)` of weighted_covariance
  * (qsrt/candidate_hessian.py:70-112) and _accumulate_hessian (qsrt/capture.py:714-731).

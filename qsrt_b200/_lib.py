@@ -27,6 +27,10 @@ _SIGNATURES = {
         _c.c_int,
         [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_size_t, _PTR],
     ),
+    "qsrtb_quantize_tiles_static": (
+        _c.c_int,
+        [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR],
+    ),
     "qsrtb_ldlq_quantize_rows": (
         _c.c_int,
         [_PTR, _PTR, _c.c_float, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,

@@ -757,3 +757,73 @@ extern "C" int qsrtb_viterbi_set_units(int units)
     g_units = units;
     return QSRTB_OK;
 }
+
+// ---- tile search without any allocation ---------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory once they are running: a serving
+// process whose memory pool has already claimed the whole GPU, or a plugin that is handed its
+// buffers by an embedding application and has no allocation rights of its own.  They cannot
+// provide the traceback scratch the regular entry point asks for.  For them the survivor rows
+// live in the fixed array below, which is part of the loaded module on every GPU that uses the
+// library (16 MiB per device, held until the process exits).
+//
+// The array gives a grid of at most 16 (K2, K3) or 32 (K4) persistent CTAs, so this entry
+// point is meant for modest batches and refuses more than QSRTB_STATIC_MAX_TILES per call.
+// All calls share the array.  The search writes every survivor row before it reads it, so
+// nothing has to be cleared between calls; but two calls that overlap on the GPU (different
+// streams, or different host threads) would overwrite each other's rows - serialise them.
+#define QSRTB_STATIC_SCRATCH_BYTES (16u << 20)
+#define QSRTB_STATIC_MAX_TILES 4096
+
+static __device__ __align__(256) uint8_t g_static_scratch[QSRTB_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint8_t* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the array on the current device.  In host code `g_static_scratch` is only
+// a handle for the runtime, not an address a kernel could use; the address is looked up once
+// per device, with that device current, and cached.
+int static_scratch_for_current_device(uint8_t** out)
+{
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaGetDevice");
+    if (device < 0 || device >= kMaxDevices) return qsrtb_fail(QSRTB_EINVAL, "device ordinal out of range");
+    if (g_static_scratch_ptr[device] == nullptr) {
+        void* address = nullptr;
+        err = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaGetSymbolAddress(static scratch)");
+        g_static_scratch_ptr[device] = static_cast<uint8_t*>(address);
+    }
+    *out = g_static_scratch_ptr[device];
+    return QSRTB_OK;
+}
+}  // namespace
+
+extern "C" int qsrtb_quantize_tiles_static(const float* tiles, int64_t n_tiles,
+                                           const uint8_t* lut_state, const uint8_t* lut_pm,
+                                           int bits, int tailbite_context, int variant,
+                                           float* out_tiles, int16_t* out_states, void* stream)
+{
+    const int bad = check_common(bits, tailbite_context, variant, n_tiles);
+    if (bad) return bad;
+    if (n_tiles > QSRTB_STATIC_MAX_TILES)
+        return qsrtb_fail(QSRTB_EINVAL,
+                          "qsrtb_quantize_tiles_static handles at most 4096 tiles per call; "
+                          "split the batch or use qsrtb_quantize_tiles with caller scratch");
+    if (n_tiles == 0) return QSRTB_OK;
+    if (!tiles || !lut_state || !lut_pm || !out_tiles || !out_states)
+        return qsrtb_fail(QSRTB_EINVAL, "null pointer");
+    uint8_t* scratch = nullptr;
+    const int status = static_scratch_for_current_device(&scratch);
+    if (status != QSRTB_OK) return status;
+    TileIO io{};
+    io.tiles = tiles;
+    io.out_tiles = out_tiles;
+    io.out_states = reinterpret_cast<uint16_t*>(out_states);
+    io.rows_mode = 0;
+    io.tiles_n = 1;
+    return dispatch(io, n_tiles, lut_state, lut_pm, bits, tailbite_context, variant, scratch,
+                    size_t(QSRTB_STATIC_SCRATCH_BYTES), static_cast<cudaStream_t>(stream));
+}

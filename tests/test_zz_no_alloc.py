@@ -1,0 +1,63 @@
+"""The allocation-free tile search (``qsrtb_quantize_tiles_static``).
+
+Some users of the library run where device memory may no longer be allocated - a serving
+process whose pool already owns the GPU, or a plugin that only receives buffers from its host
+application.  For them the library keeps a fixed 16 MiB survivor scratch inside its own image.
+This test drives that entry point through the C ABI, twice in a row on different inputs (the
+second call sees the first call's leftovers in the shared scratch), and requires bit-identical
+results to the regular entry point, which uses caller-provided scratch.
+
+Collected last (file name) so that a run stopping at the first failure has already run every
+other test; it also passes when run alone in a fresh process.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+from qsrt_b200 import _lib, tables
+from qsrt_b200 import tiles as tile_api
+
+pytestmark = pytest.mark.gpu
+
+
+def _static_encode(tiles, lut, lut_pm, bits, context, variant):
+    out = torch.empty_like(tiles)
+    states = torch.empty_like(tiles, dtype=torch.int16)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(tiles.device).cuda_stream)
+    status = _lib.lib().qsrtb_quantize_tiles_static(
+        tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits, context, variant,
+        out.data_ptr(), states.data_ptr(), stream,
+    )
+    return status, out, states
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_static_scratch_entry_matches_regular_entry_twice(cuda_device, bits):
+    codebook = tables.sqg_xor_cheb_t12_bytes(bits)
+    lut, lut_pm, abs_max = tile_api.prepared_table(codebook, bits, cuda_device)
+    variant = 1 if (bits == 2 and 0.0 < abs_max <= 16.0) else 0
+    g = torch.Generator().manual_seed(900 + bits)
+    first = torch.randn((70, 256), generator=g)
+    first[5] *= 100.0            # saturating row: takes the re-encode path of the generic arithmetic
+    second = torch.randn((33, 256), generator=g) * 2.0
+    for batch, context in ((first, 128), (second, 32)):
+        tiles = batch.to(cuda_device).contiguous()
+        expected_out, expected_states = tile_api.encode_tiles(tiles, codebook, bits, context)
+        status, out, states = _static_encode(tiles, lut, lut_pm, bits, context, variant)
+        assert status == _lib.OK, _lib.lib().qsrtb_last_error()
+        torch.cuda.synchronize(cuda_device)
+        assert torch.equal(states, expected_states)
+        assert torch.equal(out, expected_out)
+
+
+def test_static_scratch_entry_rejects_oversized_batches(cuda_device):
+    codebook = tables.sqg_xor_cheb_t12_bytes(3)
+    lut, lut_pm, _ = tile_api.prepared_table(codebook, 3, cuda_device)
+    tiles = torch.zeros((4097, 256), device=cuda_device)
+    status, _, _ = _static_encode(tiles, lut, lut_pm, 3, 128, 0)
+    assert status == _lib.EINVAL
+    assert b"4096" in _lib.lib().qsrtb_last_error()
+    status, _, _ = _static_encode(tiles[:0], lut, lut_pm, 3, 128, 0)
+    assert status == _lib.OK
