@@ -306,6 +306,8 @@ def run_b200(args) -> None:
 
     launches_before = _lib.kernel_launches()
     tile_api.search_timings = []
+    base_event = torch.cuda.Event(enable_timing=True)
+    base_event.record()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -313,7 +315,15 @@ def run_b200(args) -> None:
     clocks = sampler.stop() if rank == 0 else {}
     launches = _lib.kernel_launches() - launches_before
     torch.cuda.synchronize(device)
-    search_ms = sum(s.elapsed_time(e) for s, e, _, _ in tile_api.search_timings)
+    # Search launches of independent recursions overlap on different streams: the kernel's
+    # busy time is the union of the launch intervals, placed on one clock through a base event.
+    intervals = sorted((base_event.elapsed_time(s), base_event.elapsed_time(e)) for s, e, _, _ in tile_api.search_timings)
+    search_ms, cursor = 0.0, float("-inf")
+    for begin, end in intervals:
+        if end > cursor:
+            search_ms += end - max(begin, cursor)
+            cursor = end
+    launch_ms_sum = sum(e - b for b, e in intervals)
     search_tiles = sum(n for _, _, n, _ in tile_api.search_timings)
     search_launches = len(tile_api.search_timings)
     tile_api.search_timings = None
@@ -375,7 +385,8 @@ def run_b200(args) -> None:
             "traffic": None,
             "peak_source": "live half2 FMA probe / 3 half ops per branch metric (MEASURED_PEAKS.json holds no ALU figure)",
             "launches": search_launches,
-            "avg_launch_ms": search_ms / max(search_launches, 1),
+            "avg_launch_ms": launch_ms_sum / max(search_launches, 1),
+            "busy_ms": search_ms,
             "tiles_per_s": search_tiles / (search_ms * 1e-3) if search_ms > 0 else 0.0,
             "share_of_step": search_ms / total_ms if total_ms > 0 else None,
         },

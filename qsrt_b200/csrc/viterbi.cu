@@ -72,31 +72,43 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t b)
     return __half2float(__half(raw));
 }
 
-struct MinIdx {
+constexpr int ilog2(int n) { return n <= 1 ? 0 : 1 + ilog2(n / 2); }
+
+// Minimum of a group of candidates plus, per 16-bit lane, the bits of the winner's position
+// as full-lane masks (0xffff / 0): bit[j] is bit j of the position inside the group.
+template <int LOG>
+struct MinBits {
     __half2 m;
-    uint32_t idx;  // one predecessor index per 16-bit lane
+    uint32_t bit[LOG > 0 ? LOG : 1];
 };
 
 // Tournament over c[LO .. LO+N).  On ties the lower predecessor wins, which is what a
-// sequential scan with a strict less-than keeps.
+// sequential scan with a strict less-than keeps.  A merge costs one min, one compare and one
+// three-input select per index bit already known below it; the compare mask itself is the new
+// top bit, so no constants are folded in until the position is assembled once at the end.
 template <int LO, int N, bool RECORD, int NK>
-__device__ __forceinline__ MinIdx tournament(const __half2 (&c)[NK])
+__device__ __forceinline__ MinBits<ilog2(N)> tournament(const __half2 (&c)[NK])
 {
+    MinBits<ilog2(N)> r;
     if constexpr (N == 1) {
-        return MinIdx{c[LO], 0u};
+        r.m = c[LO];
+        r.bit[0] = 0u;
     } else {
-        const MinIdx a = tournament<LO, N / 2, RECORD, NK>(c);
-        const MinIdx b = tournament<LO + N / 2, N / 2, RECORD, NK>(c);
-        MinIdx r;
+        constexpr int LOG = ilog2(N);
+        const auto a = tournament<LO, N / 2, RECORD, NK>(c);
+        const auto b = tournament<LO + N / 2, N / 2, RECORD, NK>(c);
         r.m = __hmin2(b.m, a.m);
         if constexpr (RECORD) {
             const uint32_t lt = __hlt2_mask(b.m, a.m);
-            r.idx = (lt & (b.idx | (uint32_t(N / 2) * 0x00010001u))) | (~lt & a.idx);
+#pragma unroll
+            for (int j = 0; j < LOG - 1; ++j) r.bit[j] = (lt & b.bit[j]) | (~lt & a.bit[j]);
+            r.bit[LOG - 1] = lt;
         } else {
-            r.idx = 0u;
+#pragma unroll
+            for (int j = 0; j < LOG; ++j) r.bit[j] = 0u;
         }
-        return r;
     }
+    return r;
 }
 
 // One add-compare-select step for the calling thread's out-edges.
@@ -175,7 +187,7 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, c
                 c[k] = v;
             }
         }
-        MinIdx r = tournament<0, NK, RECORD, NK>(c);
+        auto r = tournament<0, NK, RECORD, NK>(c);
         if constexpr (MODE == MODE_K2) {
             r.m = __hsub2(r.m, shift2);
             track = __hmin2(track, r.m);
@@ -183,7 +195,12 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, c
             track = __hmax2(track, r.m);
         }
         outw[j] = h22u(r.m);
-        dec[j] = r.idx;
+        uint32_t position = 0u;
+        if constexpr (RECORD) {
+#pragma unroll
+            for (int b = 0; b < K; ++b) position |= r.bit[b] & (0x00010001u << b);
+        }
+        dec[j] = position;
     }
 
     // Store the new costs: E consecutive halves.

@@ -34,6 +34,12 @@ had_k, had_n = 128, 128
 codebook_scale = 1.24371088
 SIGMA_REG = 0.025
 
+# The reference parks the damped Hessian (and, in quantize_qsrt, the factor) in host memory to
+# save VRAM (exl3_encoder_backend.py:336-341, 2155-2157, 2829-2830): two 205 MB transfers through
+# pageable memory per 7168-wide Hessian.  With 180 GB of HBM they can stay on the device; set
+# this to False to reproduce the reference's placement exactly.
+KEEP_HESSIAN_ON_DEVICE = True
+
 finalize_capture_H_mutex = threading.Lock()
 _SHARED_INPUT_SCALES: dict = {}
 
@@ -190,7 +196,7 @@ def block_ldl(H: torch.Tensor, b: int, quant_args: dict, verbose: bool):
             )
         print(f" !! Cholesky decomp. failed, increasing diagonal damping, attempt {retries}/10")
         H.diagonal().add_(2.0 * quant_args.get("sigma_reg", SIGMA_REG) * H.diagonal().mean())
-    H_cpu = H.cpu()
+    H_cpu = H.clone() if KEEP_HESSIAN_ON_DEVICE else H.cpu()
     H.copy_(L)
     del L
     with torch.cuda.device(H.device):
@@ -238,7 +244,8 @@ def _factor_capture_H(H_data: dict, H: torch.Tensor, su: torch.Tensor, quant_arg
     else:
         L, H = block_ldl(H, 16, quant_args, verbose)
     H_data["L"] = L
-    H = H.cpu()
+    if not KEEP_HESSIAN_ON_DEVICE:
+        H = H.cpu()
     H_data["H"] = H
     H_data["su"] = su
     H_data["finalized"] = True
@@ -629,10 +636,13 @@ def _mixed_plan(size_k: int, size_n: int, quant_args: dict, device):
     return per_tile
 
 
-def _ldlq_core(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, pb=None):
-    """The reference's reverse block recursion (exl3_encoder_backend.py:470-539, 2020-2068):
-    spans of ``buf_size_k`` rows from the bottom up, 16-row blocks inside a span, the same
-    two GEMM calls, and one fused encode launch per rate present in the 16-row step."""
+def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, out: dict):
+    """Generator form of the reference's reverse block recursion
+    (exl3_encoder_backend.py:470-539, 2020-2068): spans of ``buf_size_k`` rows from the bottom
+    up, 16-row blocks inside a span, the same two GEMM calls, and one fused encode launch per
+    rate present in the 16-row step.  Yields after every 16-row step (nothing synchronises), so
+    several recursions can be interleaved on different streams; ``out`` receives
+    ``weight_q`` and ``encoded``."""
 
     assert weights.ndim == 3 and Ls.ndim == 3
     batch, size_k, size_n = weights.shape
@@ -642,40 +652,108 @@ def _ldlq_core(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, 
     buf_size_k = max(quant_args.get("buf_size_k", 128), 16)
     assert buf_size_k % 16 == 0 and size_k % buf_size_k == 0
     tiles_k, tiles_n = size_k // 16, size_n // 16
+    tf32 = bool(quant_args.get("ldlq_tf32", False))
 
     prod_cache = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
     weight_q = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
     err = torch.zeros((batch, size_k, size_n), dtype=torch.float, device=device)
     encoded = torch.zeros((batch, tiles_k, tiles_n, 256), dtype=torch.short, device=device)
-    allow_tf32 = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = bool(quant_args.get("ldlq_tf32", False))
-    try:
-        p_row = 0
-        for j in range(size_k, 0, -buf_size_k):
-            i = j - buf_size_k
-            for bj in range(buf_size_k, 0, -16):
-                bi = bj - 16
-                comp = prod_cache[:, i + bi:i + bj]
-                if bj < buf_size_k:
-                    # compensation from the rows already encoded inside this span
-                    comp.baddbmm_(Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
-                for bits, tile_map in plan((i + bi) // 16):
-                    _quantize_rows(
-                        weights[:, i + bi:], comp, multiplier, weight_q[:, i + bi:], err[:, i + bi:],
-                        encoded[:, (i + bi) // 16], quant_args, bits,
-                        batch=batch, n=size_n, ld=size_n, w_stride=size_k * size_n,
-                        comp_ld=size_n, comp_stride=size_k * size_n,
-                        state_stride=tiles_k * tiles_n * 256, tile_map=tile_map,
-                    )
-                if pb:
-                    p_row += 1
-                    pb.update(p_row)
-            if i > 0:
+    out["weight_q"], out["encoded"] = weight_q, encoded
+
+    def gemm(target, a, b):
+        allow = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        try:
+            target.baddbmm_(a, b)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = allow
+
+    for j in range(size_k, 0, -buf_size_k):
+        i = j - buf_size_k
+        for bj in range(buf_size_k, 0, -16):
+            bi = bj - 16
+            comp = prod_cache[:, i + bi:i + bj]
+            if bj < buf_size_k:
+                # compensation from the rows already encoded inside this span
+                gemm(comp, Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
+            for bits, tile_map in plan((i + bi) // 16):
+                _quantize_rows(
+                    weights[:, i + bi:], comp, multiplier, weight_q[:, i + bi:], err[:, i + bi:],
+                    encoded[:, (i + bi) // 16], quant_args, bits,
+                    batch=batch, n=size_n, ld=size_n, w_stride=size_k * size_n,
+                    comp_ld=size_n, comp_stride=size_k * size_n,
+                    state_stride=tiles_k * tiles_n * 256, tile_map=tile_map,
+                )
+            if bj == 16 and i > 0:
                 # cache the span's error for every row block still to be encoded
-                prod_cache[:, :i].baddbmm_(Ls[:, i:j, :i].transpose(1, 2), err[:, i:j])
-    finally:
-        torch.backends.cuda.matmul.allow_tf32 = allow_tf32
-    return weight_q, encoded
+                gemm(prod_cache[:, :i], Ls[:, i:j, :i].transpose(1, 2), err[:, i:j])
+            yield
+
+
+def _ldlq_core(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, pb=None):
+    out: dict = {}
+    for step, _ in enumerate(_ldlq_steps(weights, Ls, quant_args, plan, out), start=1):
+        if pb:
+            pb.update(step)
+    return out["weight_q"], out["encoded"]
+
+
+_side_stream_cache: dict[str, list] = {}
+
+
+def _side_streams(device: torch.device, count: int) -> list:
+    """Long-lived side streams (their survivor scratch and cuBLAS workspaces are created once)."""
+
+    pool = _side_stream_cache.setdefault(str(device), [])
+    while len(pool) < count:
+        pool.append(torch.cuda.Stream(device=device))
+    return pool[:count]
+
+
+def ldlq_concurrent(jobs: list[tuple[torch.Tensor, torch.Tensor, dict]]):
+    """Run several independent stacked LDLQ recursions at once, each on its own stream.
+
+    A 16-row step offers only ``batch * n / 16`` tiles; one persistent search launch then leaves
+    part of the GPU idle in its last wave.  Interleaving independent recursions (for example the
+    gate/up stack and the down stack of an expert batch) lets the CTAs of one launch fill the
+    tail of the other.  Returns ``[(weight_q, encoded), ...]`` in job order; on return the
+    current stream has been made to wait for all of them."""
+
+    if not jobs:
+        return []
+    device = jobs[0][0].device
+    current = torch.cuda.current_stream(device)
+    ready = torch.cuda.Event()
+    ready.record(current)
+    streams = _side_streams(device, len(jobs)) if len(jobs) > 1 else [current]
+    outs: list[dict] = [{} for _ in jobs]
+    gens = []
+    for (weights, Ls, quant_args), stream, out in zip(jobs, streams, outs):
+        stream.wait_event(ready)
+        with torch.cuda.stream(stream):
+            gens.append(_ldlq_steps(weights, Ls, quant_args, _uniform_plan(int(quant_args["K"])), out))
+    alive = list(range(len(jobs)))
+    # advance the longer recursions proportionally more often so that all finish together
+    lengths = [w.shape[1] // 16 for w, _, _ in jobs]
+    progress = [0] * len(jobs)
+    while alive:
+        k = min(alive, key=lambda idx: (progress[idx] / lengths[idx], idx))
+        with torch.cuda.stream(streams[k]):
+            try:
+                next(gens[k])
+                progress[k] += 1
+            except StopIteration:
+                alive.remove(k)
+    for stream, (weights, Ls, _), out in zip(streams, jobs, outs):
+        if stream is not current:
+            done = torch.cuda.Event()
+            done.record(stream)
+            current.wait_event(done)
+            for t in (weights, Ls):
+                t.record_stream(stream)      # allocated on the caller's stream, read on the side stream
+            for t in (out["weight_q"], out["encoded"]):
+                t.record_stream(current)     # allocated on the side stream, consumed by the caller
+    return [(o["weight_q"], o["encoded"]) for o in outs]
 
 
 def ldlq_batched(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, pb=None):
@@ -825,7 +903,7 @@ def quantize_qsrt(weight: torch.Tensor, H_data: dict, quant_args: dict, return_w
     if H_diag is not None:
         H_diag = H_diag.to(device)
     sv = output_signs(n, device, quant_args)
-    if H_data["L"] is not None:
+    if H_data["L"] is not None and not KEEP_HESSIAN_ON_DEVICE:
         H_data["L"] = H_data["L"].cpu()
     if swap_to_device is not None:
         weight = weight.to(swap_to_device)
@@ -877,9 +955,31 @@ def quantize_uniform_batch(weights: list[torch.Tensor], H_datas: list[dict], qua
     Shared Hessian (the same ``H_data`` object for every tensor): the regularised weights are
     concatenated along out_features and run through one LDLQ pass.  Distinct Hessians over
     same-shape tensors: the tensors are stacked and every 16-row step encodes all of their
-    tiles in one launch.  Returns ``[(proxy_err, out_tensors), ...]``.
+    tiles in one launch.  (Generalisation: runs of tensors that share an ``H_data`` object are
+    concatenated, and equally shaped runs are stacked - e.g. the gate/up pairs of several
+    experts.)  Returns ``[(proxy_err, out_tensors), ...]``.
     """
 
+    return quantize_uniform_groups([(weights, H_datas, quant_args_list)], verbose=verbose)[0]
+
+
+def quantize_uniform_groups(groups: list[tuple[list[torch.Tensor], list[dict], list[dict]]], verbose: bool = False):
+    """Several ``quantize_uniform_batch`` groups whose LDLQ recursions run concurrently on
+    separate streams (``ldlq_concurrent``).  Per group the semantics are exactly those of
+    ``quantize_uniform_batch``; the groups must be independent of each other."""
+
+    states = [_uniform_prepare(w, h, q, verbose) for w, h, q in groups]
+    jobs, owners = [], []
+    for gi, st in enumerate(states):
+        if st["job"] is not None:
+            jobs.append(st["job"])
+            owners.append(gi)
+    for gi, (weight_q, encoded) in zip(owners, ldlq_concurrent(jobs)):
+        states[gi]["weight_q"], states[gi]["encoded"] = weight_q, encoded
+    return [_uniform_finish(st) for st in states]
+
+
+def _uniform_prepare(weights, H_datas, quant_args_list, verbose):
     if any("mixed_rate_axis" in qa or "mixed_tile_bits" in qa for qa in quant_args_list):
         raise ValueError("mixed-rate LDLQ is currently supported by quantize_qsrt, not the same-K batch API")
     for qa in quant_args_list:
@@ -887,8 +987,6 @@ def quantize_uniform_batch(weights: list[torch.Tensor], H_datas: list[dict], qua
     n_t = len(weights)
     qa0 = quant_args_list[0]
     device = torch.device(qa0["devices"][0])
-    shared_H = all(hd is H_datas[0] for hd in H_datas)
-    assert shared_H or all(w.shape == weights[0].shape for w in weights)
     assert all(w.shape[0] == weights[0].shape[0] for w in weights)
     assert all(qa["K"] == qa0["K"] for qa in quant_args_list)
     results: list = [None] * n_t
@@ -904,8 +1002,10 @@ def quantize_uniform_batch(weights: list[torch.Tensor], H_datas: list[dict], qua
     for t in range(n_t):
         if finalized[t] is None:
             results[t] = quantize_qsrt(weights[t], H_datas[t], quant_args_list[t], False, None, verbose)[1:]
+    state = {"results": results, "batch_idx": batch_idx, "finalized": finalized, "job": None,
+             "quant_args_list": quant_args_list, "device": device}
     if not batch_idx:
-        return results
+        return state
 
     regs = {}
     for t in batch_idx:
@@ -934,43 +1034,54 @@ def quantize_uniform_batch(weights: list[torch.Tensor], H_datas: list[dict], qua
             regs[t][1] /= g_scale
         g_scales[t] = g_scale
 
-    if shared_H:
-        L = finalized[batch_idx[0]][1].to(device)
-        widths = [regs[t][0].shape[1] for t in batch_idx]
-        weight_r_cat = torch.cat([regs[t][0] for t in batch_idx], dim=1)
-        for t in batch_idx:
-            regs[t][0] = None
-        weight_q_cat, encoded_cat = ldlq(weight_r_cat, L, qa0)
-        del L
-        weight_rs = list(torch.split(weight_r_cat, widths, dim=1))
-        weight_qs = list(torch.split(weight_q_cat, widths, dim=1))
-        encodeds = list(torch.split(encoded_cat, [w // 16 for w in widths], dim=1))
-    else:
-        Ls = torch.stack([finalized[t][1].to(device) for t in batch_idx])
-        weight_r_stack = torch.stack([regs[t][0] for t in batch_idx])
-        for t in batch_idx:
-            regs[t][0] = None
-        weight_q_stack, encoded_stack = ldlq_batched(weight_r_stack, Ls, qa0)
-        del Ls
-        weight_rs = list(weight_r_stack.unbind(0))
-        weight_qs = list(weight_q_stack.unbind(0))
-        encodeds = list(encoded_stack.unbind(0))
+    # runs of consecutive tensors sharing one H_data object are concatenated along out_features
+    runs: list[list[int]] = []
+    for t in batch_idx:
+        if runs and H_datas[runs[-1][0]] is H_datas[t]:
+            runs[-1].append(t)
+        else:
+            runs.append([t])
+    cats = [torch.cat([regs[t][0] for t in run], dim=1) if len(run) > 1 else regs[run[0]][0] for run in runs]
+    assert all(c.shape == cats[0].shape for c in cats), "tensor groups with distinct Hessians must have one shape"
+    for t in batch_idx:
+        regs[t][0] = None
+    weight_r_stack = torch.stack(cats) if len(cats) > 1 else cats[0].unsqueeze(0)
+    del cats
+    Ls = [finalized[run[0]][1].to(device) for run in runs]
+    Ls_stack = torch.stack(Ls) if len(Ls) > 1 else Ls[0].unsqueeze(0)
+    del Ls
+    state.update({"regs": regs, "g_scales": g_scales, "runs": runs, "weight_r": weight_r_stack,
+                  "job": (weight_r_stack, Ls_stack, qa0)})
+    return state
 
-    Hd = None
-    for bi, t in enumerate(batch_idx):
-        qa = quant_args_list[t]
-        _, su, sv, apply_out_scales = regs[t]
-        if not shared_H or Hd is None:
-            Hd = finalized[t][0].to(device)
-        num = block_trace(weight_rs[bi] - weight_qs[bi], Hd)
-        den = block_trace(weight_rs[bi], Hd)
-        proxy_err = num / max(den, 1e-8)
-        weight_rs[bi] = None
-        weight_qs[bi] = None
-        suh = su.flatten().contiguous().to(dtype=torch.half, copy=True)
-        svh = sv.flatten().contiguous().to(dtype=torch.half, copy=True)
-        trellis = pack_trellis(encodeds[bi].contiguous(), qa)
-        encodeds[bi] = None
-        qa.update({"apply_out_scales": apply_out_scales, "g_scale": g_scales[t], "q_fallback": False})
-        results[t] = (proxy_err, {"suh": suh, "svh": svh, "trellis": trellis})
+
+def _uniform_finish(state):
+    results = state["results"]
+    if state["job"] is None:
+        return results
+    device = state["device"]
+    quant_args_list = state["quant_args_list"]
+    finalized, regs, runs = state["finalized"], state["regs"], state["runs"]
+    weight_r_stack, weight_q_stack, encoded_stack = state["weight_r"], state["weight_q"], state["encoded"]
+    state["job"] = None  # drop the stacked factors
+    for ri, run in enumerate(runs):
+        Hd = finalized[run[0]][0].to(device)
+        col = 0
+        for t in run:
+            qa = quant_args_list[t]
+            _, su, sv, apply_out_scales = regs[t]
+            width = sv.shape[1]
+            w_r = weight_r_stack[ri, :, col:col + width]
+            w_q = weight_q_stack[ri, :, col:col + width]
+            enc = encoded_stack[ri, :, col // 16:(col + width) // 16]
+            col += width
+            num = block_trace(w_r - w_q, Hd)
+            den = block_trace(w_r, Hd)
+            proxy_err = num / max(den, 1e-8)
+            suh = su.flatten().contiguous().to(dtype=torch.half, copy=True)
+            svh = sv.flatten().contiguous().to(dtype=torch.half, copy=True)
+            trellis = pack_trellis(enc.contiguous(), qa)
+            qa.update({"apply_out_scales": apply_out_scales, "g_scale": state["g_scales"][t], "q_fallback": False})
+            results[t] = (proxy_err, {"suh": suh, "svh": svh, "trellis": trellis})
+        del Hd
     return results

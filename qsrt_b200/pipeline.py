@@ -137,49 +137,63 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
         return []
     device = torch.device(device)
     results: list[ExpertPayload] = []
-    gate_up = []
-    weights_sq = []
-    middles = []
-    for ex in experts:
-        w = ex.gates.float().square()
-        weights_sq.append(w)
+    weights_sq = [ex.gates.float().square() for ex in experts]
+
+    def seed_of(ex, offset):
+        return 6 * (layer_seed * 100003 + ex.expert_id) + offset
+
+    # group A: gate and up of every expert; a pair shares its expert's H13
+    a_weights, a_h, a_args = [], [], []
+    for ex, w in zip(experts, weights_sq):
         h13, _ = hessian.weighted_covariance(ex.rows, w, device=device, return_cpu=False)
         shared = encoder.make_shared_h(ex.w1.shape[1], device, h13)
         del h13
-        seed = 2 * (layer_seed * 100003 + ex.expert_id) * 3
-        args1 = quant_args_for(bits, device, seed=seed, sv_seed=seed + 1, sigma_reg=sigma_reg, tailbite_context=tailbite_context)
-        args3 = quant_args_for(bits, device, seed=seed, sv_seed=seed + 2, sigma_reg=sigma_reg, tailbite_context=tailbite_context)
-        out = encoder.quantize_uniform_batch(
-            [ex.w1.T.float().contiguous(), ex.w3.T.float().contiguous()], [shared, shared], [args1, args3]
-        )
-        p1, p3 = _payload(out[0], args1), _payload(out[1], args3)
-        gate_up.append((p1, p3))
-        if down_from_reconstruction:
-            middle = gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
-        else:
-            middle = gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation)
-        middles.append(middle)
+        for matrix, offset in ((ex.w1, 1), (ex.w3, 2)):
+            a_weights.append(matrix.T.float().contiguous())
+            a_h.append(shared)
+            a_args.append(quant_args_for(bits, device, seed=seed_of(ex, 0), sv_seed=seed_of(ex, offset),
+                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context))
 
-    down_weights, down_h, down_args, evidence = [], [], [], []
-    for ex, w, middle in zip(experts, weights_sq, middles):
-        local_h2, _ = hessian.weighted_covariance(middle, w, device=device, return_cpu=False)
-        h2, info = hessian.adaptive_identity_shrinkage(local_h2, w, max_local_alpha=h2_max_local_alpha)
-        del local_h2
-        down_h.append(encoder.make_shared_h(ex.w2.shape[1], device, h2))
-        del h2
-        seed = 2 * (layer_seed * 100003 + ex.expert_id) * 3 + 3
-        down_args.append(quant_args_for(bits, device, seed=seed, sv_seed=seed + 1, sigma_reg=sigma_reg,
-                                        tailbite_context=tailbite_context))
-        down_weights.append(ex.w2.T.float().contiguous())
-        evidence.append(info)
-    down_out = encoder.quantize_uniform_batch(down_weights, down_h, down_args)
+    def down_group(middles):
+        b_weights, b_h, b_args, infos = [], [], [], []
+        for ex, w, middle in zip(experts, weights_sq, middles):
+            local_h2, _ = hessian.weighted_covariance(middle, w, device=device, return_cpu=False)
+            h2, info = hessian.adaptive_identity_shrinkage(local_h2, w, max_local_alpha=h2_max_local_alpha)
+            del local_h2
+            b_h.append(encoder.make_shared_h(ex.w2.shape[1], device, h2))
+            del h2
+            b_args.append(quant_args_for(bits, device, seed=seed_of(ex, 3), sv_seed=seed_of(ex, 4),
+                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context))
+            b_weights.append(ex.w2.T.float().contiguous())
+            infos.append(info)
+        return (b_weights, b_h, b_args), infos
+
+    if down_from_reconstruction:
+        a_out = encoder.quantize_uniform_batch(a_weights, a_h, a_args)
+        gate_up = [(_payload(a_out[2 * i], a_args[2 * i]), _payload(a_out[2 * i + 1], a_args[2 * i + 1]))
+                   for i in range(len(experts))]
+        middles = [gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
+                   for ex, (p1, p3) in zip(experts, gate_up)]
+        group_b, evidence = down_group(middles)
+        down_args = group_b[2]
+        down_out = encoder.quantize_uniform_batch(*group_b)
+    else:
+        middles = [gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation) for ex in experts]
+        group_b, evidence = down_group(middles)
+        down_args = group_b[2]
+        # gate/up and down do not depend on each other here: their recursions run concurrently
+        a_out, down_out = encoder.quantize_uniform_groups([(a_weights, a_h, a_args), group_b])
+        gate_up = [(_payload(a_out[2 * i], a_args[2 * i]), _payload(a_out[2 * i + 1], a_args[2 * i + 1]))
+                   for i in range(len(experts))]
 
     for ex, (p1, p3), res, args, w, middle, info in zip(experts, gate_up, down_out, down_args, weights_sq, middles, evidence):
         p2 = _payload(res, args)
         payload = ExpertPayload(ex.expert_id, bits, p1, p3, p2, evidence=info)
         payload.payload_bytes = sum(p.trellis.numel() * 2 + p.suh.numel() * 2 + p.svh.numel() * 2 for p in (p1, p3, p2))
         if score:
-            teacher = middle @ ex.w2.float().T
+            source_middle = middle if not down_from_reconstruction else gated_middle(
+                ex.rows.float(), ex.w1.float(), ex.w3.float(), activation)
+            teacher = source_middle @ ex.w2.float().T
             decoded_mid = gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
             student = decoded_mid @ decode_matrix(p2).T
             payload.routed_sse = float(((student - teacher).double().square().sum(dim=1) * w.double()).sum())

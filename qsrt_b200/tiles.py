@@ -53,7 +53,7 @@ class timed_search:
 
 
 _tables: dict[tuple[str, int, int], tuple[torch.Tensor, torch.Tensor, torch.Tensor, float]] = {}
-_scratch: dict[tuple[str, int], torch.Tensor] = {}
+_scratch: dict[tuple[str, int, int], torch.Tensor] = {}
 
 
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
@@ -94,9 +94,10 @@ def prepared_table(codebook: torch.Tensor, bits: int, device: torch.device):
 
 
 def traceback_scratch(device: torch.device, bits: int) -> torch.Tensor:
-    """Per-device survivor scratch: one slice per resident CTA of the persistent grid."""
+    """Survivor scratch of the current stream: one slice per resident CTA of the persistent
+    grid.  Keyed by stream so that searches enqueued on different streams never share rows."""
 
-    key = (str(device), bits)
+    key = (str(device), bits, torch.cuda.current_stream(device).cuda_stream)
     buffer = _scratch.get(key)
     if buffer is None:
         wanted = ctypes.c_size_t(0)
