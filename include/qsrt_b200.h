@@ -118,6 +118,17 @@ int qsrtb_hadamard128(float* x, int batch, int rows, int cols, int ld, int64_t x
                       int scale_divide, int scale_after, float* row_sumsq, int64_t sumsq_stride,
                       void* stream);
 
+/* ---- R2: signed block Walsh-Hadamard of the coupled gate/up/down coordinates -------------
+ * Replaces block_hadamard / signed_block_hadamard (qsrt/qsrt_coupled.py:49-132) on a row-major
+ * float32 matrix, in place: along `axis` (1 = within rows, 0 = within columns) every block of
+ * `block_size` (128, 256 or 512) becomes H(block * signs) / sqrt(block_size) ("D H",
+ * sign_after = 0) or H(block) / sqrt(block_size) * signs (its inverse "H D", sign_after = 1);
+ * signs may be NULL.  Butterfly order and the true division match the reference's float32
+ * CPU arithmetic bit for bit.
+ */
+int qsrtb_signed_block_hadamard(float* x, int64_t rows, int cols, int ld, int axis, int block_size,
+                                const float* signs, int sign_after, void* stream);
+
 /* Column sums of squares of `batch` matrices (the out-channel RMS of regularize,
  * qsrt/exl3_encoder_backend.py:2508-2521, 2634).  workspace: batch*ceil(rows/256)*cols floats. */
 int qsrtb_col_sumsq(const float* x, int batch, int rows, int cols, int ld, int64_t x_stride,

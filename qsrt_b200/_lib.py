@@ -46,6 +46,9 @@ _SIGNATURES = {
         [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _c.c_int, _PTR, _c.c_int64,
          _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int64, _PTR],
     ),
+    "qsrtb_signed_block_hadamard": (
+        _c.c_int, [_PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _PTR]
+    ),
     "qsrtb_col_sumsq": (
         _c.c_int,
         [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _PTR, _c.c_int64, _PTR,
@@ -70,6 +73,7 @@ _KERNELS_PER_CALL = {
     "qsrtb_viterbi_set_units": 0,
     "qsrtb_col_sumsq": 2,
     "qsrtb_block_ldl_normalize": 2,
+    "qsrtb_signed_block_hadamard": 1,
 }
 launch_counts: dict[str, int] = {}
 

@@ -72,7 +72,10 @@ def situ(gate: torch.Tensor, up: torch.Tensor, *, beta: float = 4.0, linear_beta
     return (gate_value * up_value).to(gate.dtype)
 
 
-def gated_middle(rows: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+def gated_middle(rows: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, activation: str = "silu",
+                 execution=None) -> torch.Tensor:
+    if execution is not None:
+        return execution.decode_middle(rows, w1, w3, activation)
     gate = rows @ w1.T
     up = rows @ w3.T
     if activation == "silu":
@@ -130,12 +133,25 @@ def verify_payload_roundtrip(payload: MatrixPayload) -> bool:
 def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch.device, layer_seed: int = 0,
                         sigma_reg: float = encoder.SIGMA_REG, tailbite_context: int = 128,
                         activation: str = "silu", down_from_reconstruction: bool = False,
-                        score: bool = True, h2_max_local_alpha: float = 0.75) -> list[ExpertPayload]:
-    """Encode a batch of experts at one uniform rate; see the module docstring for the flow."""
+                        score: bool = True, h2_max_local_alpha: float = 0.75,
+                        coupled_spec=None) -> list[ExpertPayload]:
+    """Encode a batch of experts at one uniform rate; see the module docstring for the flow.
+
+    With ``coupled_spec`` (a ``coupled.CoupledHadamardSpec``) every expert is first moved into
+    the coupled signed block-Hadamard coordinates (``encode_coupled_weights``), its routed rows
+    with it (``transform_inputs``), the middle activation is evaluated through
+    ``decode_middle`` and the routed error through ``decode_output``
+    (``qsrt/pack/qsrt_candidates.py:1157-1180``); the payloads then describe the coupled
+    matrices."""
 
     if not experts:
         return []
     device = torch.device(device)
+    if coupled_spec is not None:
+        return _encode_coupled_batch(experts, coupled_spec, bits=bits, device=device, layer_seed=layer_seed,
+                                     sigma_reg=sigma_reg, tailbite_context=tailbite_context,
+                                     activation=activation, down_from_reconstruction=down_from_reconstruction,
+                                     score=score, h2_max_local_alpha=h2_max_local_alpha)
     results: list[ExpertPayload] = []
     weights_sq = [ex.gates.float().square() for ex in experts]
 
@@ -172,13 +188,15 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
         a_out = encoder.quantize_uniform_batch(a_weights, a_h, a_args)
         gate_up = [(_payload(a_out[2 * i], a_args[2 * i]), _payload(a_out[2 * i + 1], a_args[2 * i + 1]))
                    for i in range(len(experts))]
-        middles = [gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
+        middles = [gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation,
+                                getattr(ex, "execution", None))
                    for ex, (p1, p3) in zip(experts, gate_up)]
         group_b, evidence = down_group(middles)
         down_args = group_b[2]
         down_out = encoder.quantize_uniform_batch(*group_b)
     else:
-        middles = [gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation) for ex in experts]
+        middles = [gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation,
+                                getattr(ex, "execution", None)) for ex in experts]
         group_b, evidence = down_group(middles)
         down_args = group_b[2]
         # gate/up and down do not depend on each other here: their recursions run concurrently
@@ -200,3 +218,35 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
             payload.routed_energy = float((teacher.double().square().sum(dim=1) * w.double()).sum())
         results.append(payload)
     return results
+
+
+def _encode_coupled_batch(experts, spec, *, score, activation, **kwargs):
+    from . import coupled
+
+    moved, executions, teachers = [], [], []
+    for ex in experts:
+        execution = coupled.CoupledHadamardExecution(hidden=ex.w1.shape[1], intermediate=ex.w1.shape[0], spec=spec)
+        c1, c3, c2 = coupled.encode_coupled_weights((ex.w1, ex.w3, ex.w2), spec)
+        rows = execution.transform_inputs(ex.rows)
+        moved.append(_CoupledSource(c1, c3, c2, rows, ex.gates, ex.expert_id, execution, activation))
+        executions.append(execution)
+        if score:
+            teachers.append(gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation) @ ex.w2.float().T)
+    payloads = encode_expert_batch(moved, score=False, activation=activation, **kwargs)
+    if score:
+        for payload, src, execution, teacher, ex in zip(payloads, moved, executions, teachers, experts):
+            decoded = (decode_matrix(payload.w1), decode_matrix(payload.w3), decode_matrix(payload.w2))
+            student = execution.execute(ex.rows.float(), decoded, activation)
+            w = ex.gates.float().square().double()
+            payload.routed_sse = float(((student - teacher).double().square().sum(dim=1) * w).sum())
+            payload.routed_energy = float((teacher.double().square().sum(dim=1) * w).sum())
+    return payloads
+
+
+@dataclass
+class _CoupledSource(ExpertSource):
+    """An expert already moved to coupled coordinates: its middle activation is evaluated by the
+    coupled execution (inverse pre-activation transform, activation, post-activation transform)."""
+
+    execution: object = None
+    activation: str = "silu"

@@ -83,3 +83,17 @@ def reference_quantize_tiles(tiles: torch.Tensor, lut_state: torch.Tensor, bits:
     ext.quantize_tiles_sqg(tiles.contiguous(), out, idx, costs, trace, lut, bits, context, abs_max)
     torch.cuda.synchronize(device)
     return out, idx
+
+
+def coupled_inputs(hidden: int = 512, inter: int = 128, rows: int = 48, seed: int = 77):
+    """Seeded expert triplet, routed rows and Hessians for the coupled-coordinate fixtures."""
+
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    w1 = torch.randn((inter, hidden), generator=g) * 0.02
+    w3 = torch.randn((inter, hidden), generator=g) * 0.02
+    w2 = torch.randn((hidden, inter), generator=g) * 0.02
+    x = torch.randn((rows, hidden), generator=g)
+    h13 = (x.T @ x / rows).float()
+    m = torch.randn((rows, inter), generator=g)
+    h2 = (m.T @ m / rows).float()
+    return w1, w3, w2, x, h13, h2

@@ -124,3 +124,28 @@ def test_down_from_reconstruction_flow(cuda_device):
     assert torch.equal(a.w1.trellis, b.w1.trellis)          # gate/up do not depend on the flag
     assert not torch.equal(a.w2.trellis, b.w2.trellis)      # the down Hessian does
     assert pipeline.verify_payload_roundtrip(b.w2)
+
+
+def test_coupled_coordinate_flow(cuda_device):
+    """Coupled-Hadamard layer flow: coupled transform, gate/up first, reconstructed activations
+    form the down covariance, then down; scored in source coordinates."""
+
+    from qsrt_b200 import coupled
+
+    experts = _tiny_experts(cuda_device, count=1, hidden=512, inter=128, tokens=500)
+    spec = coupled.CoupledHadamardSpec(intermediate_draw=0)
+    plain = pipeline.encode_expert_batch(experts, bits=3, device=cuda_device, sigma_reg=1e-2)[0]
+    moved = pipeline.encode_expert_batch(experts, bits=3, device=cuda_device, sigma_reg=1e-2, coupled_spec=spec,
+                                         down_from_reconstruction=True)[0]
+    for mp in (moved.w1, moved.w3, moved.w2):
+        assert pipeline.verify_payload_roundtrip(mp)
+    assert 0.0 < moved.routed_sse < moved.routed_energy
+    # same expert, same rate: the two coordinate systems must give errors of the same order
+    assert 0.3 < (moved.routed_sse / moved.routed_energy) / (plain.routed_sse / plain.routed_energy) < 3.0
+    # decoding the coupled payload and executing it reproduces the teacher to encode accuracy
+    ex = experts[0]
+    execution = coupled.CoupledHadamardExecution(hidden=512, intermediate=128, spec=spec)
+    decoded = tuple(pipeline.decode_matrix(m) for m in (moved.w1, moved.w3, moved.w2))
+    out = execution.execute(ex.rows.float(), decoded, "silu")
+    teacher = pipeline.gated_middle(ex.rows.float(), ex.w1, ex.w3, "silu") @ ex.w2.T
+    assert float((out - teacher).norm() / teacher.norm()) < 0.35
