@@ -50,7 +50,7 @@ def parse_args():
 # reference arm: the CPU restatement, all host threads, bounded sample per step
 # --------------------------------------------------------------------------------------
 
-def cpu_sample_inputs(seed: int, k: int = 256, n: int = 128):
+def cpu_sample_inputs(seed: int, k: int = 128, n: int = 128):
     import numpy as np
 
     rng = np.random.default_rng(seed)
@@ -71,8 +71,9 @@ def run_reference(args) -> None:
 
     oracle.build_c_oracle()
     cores = os.cpu_count() or 1
+    oracle.DEFAULT_THREADS = cores  # torchrun exports OMP_NUM_THREADS=1
     lut = oracle.sqg_xor_cheb_t12_bytes(BITS)
-    k, n = 256, 128
+    k, n = 128, 128
     times = []
     for step in range(args.warmup + args.steps):
         weight, hessian, su, sv = cpu_sample_inputs(9000 + step, k, n)
@@ -412,6 +413,7 @@ def cpu_tile_baseline(payload) -> dict:
 
     oracle.build_c_oracle()
     cores = os.cpu_count() or 1
+    oracle.DEFAULT_THREADS = cores
     lut = tables.sqg_xor_cheb_t12_bytes(BITS)
     states = codec.unpack_trellis_states(payload.w1.trellis[:4], BITS)
     work = codec.decode_regularized_weight(states, lut=lut).cpu().numpy()

@@ -208,6 +208,10 @@ def tiles_to_matrix(tiles: np.ndarray) -> np.ndarray:
 
 VARIANT_AUTO, VARIANT_GENERIC, VARIANT_K2 = 0, 1, 2
 
+# OpenMP threads used when a call does not say (0 = the OpenMP default, which launchers such
+# as torchrun pin to 1 through OMP_NUM_THREADS).
+DEFAULT_THREADS = 0
+
 
 def quantize_tiles(
     tiles: np.ndarray,
@@ -234,7 +238,7 @@ def quantize_tiles(
     idx = np.empty(tiles.shape, dtype=np.uint16)
     status = _lib().qsrt_oracle_quantize_tiles(
         tiles.ctypes.data, tiles.shape[0], lut.ctypes.data, int(bits), int(tailbite_context),
-        int(variant), out.ctypes.data, idx.ctypes.data, int(threads),
+        int(variant), out.ctypes.data, idx.ctypes.data, int(threads or DEFAULT_THREADS),
     )
     if status != 0:
         raise ValueError(f"oracle tile encoder rejected its arguments (status {status})")
