@@ -1,0 +1,108 @@
+"""Microbenchmarks of the memory- and FLOP-bound helper kernels at the headline shapes.
+
+    python -m qsrt_b200.bench_kernels [--only NAME] [--iters 5]
+
+Prints one JSON line per kernel with its algorithmic bytes (or flops) per launch, the CUDA-event
+time and the achieved GB/s (or TFLOP/s).  Shapes: gate/up in encoder orientation [7168, 2048],
+Hessian 7168 x 7168; out-features default to 8192 (four matrices side by side) so that every
+input exceeds the L2, which is also flushed between timed iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import codec, coupled, encoder, hessian, tables
+
+
+_flush = None
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    """Median CUDA-event time; a 512 MB write between iterations evicts the 126 MB L2."""
+
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda:0")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        _flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def main() -> None:
+    p = argparse.ArgumentParser()
+    p.add_argument("--only", default=None)
+    p.add_argument("--iters", type=int, default=5)
+    p.add_argument("--k", type=int, default=7168)
+    p.add_argument("--n", type=int, default=8192, help="out-features; 8192 = four stacked 2048-wide matrices")
+    p.add_argument("--rows", type=int, default=4096)
+    args = p.parse_args()
+    dev = torch.device("cuda:0")
+    k, n = args.k, args.n
+    g = torch.Generator(device=dev).manual_seed(1)
+    w = torch.randn((k, n), device=dev, generator=g)
+    sv = torch.rand(n, device=dev, generator=g) + 0.5
+    su = torch.rand(k, device=dev, generator=g) + 0.5
+    sums = torch.empty(k, device=dev)
+    h = torch.randn((k, k), device=dev, generator=g)
+    x = torch.randn((args.rows, k), device=dev, generator=g)
+    wts = torch.rand(args.rows, device=dev, generator=g)
+    acc = torch.empty((k, k), device=dev)
+    bits = 3
+    lut = tables.sqg_xor_cheb_t12_bytes(bits).to(dev)
+    states = torch.randint(-32768, 32767, (k // 16, n // 16, 256), device=dev, dtype=torch.int16, generator=g)
+    packed = codec.pack_trellis_edges(states, bits)
+    tiles = states.shape[0] * states.shape[1]
+    signs_n = torch.ones(n, device=dev)
+    signs_k = torch.ones(k, device=dev)
+
+    cases = {
+        "hadamard_rows (divide by sv + had_r + row sums)":
+            (lambda: encoder._hadamard(w, 1, sv, per_col=True, divide=True, row_sumsq=sums), 8 * k * n, "B"),
+        "hadamard_cols (divide by su + had_l)":
+            (lambda: encoder._hadamard(w, 0, su, per_col=False, divide=True), 8 * k * n, "B"),
+        "hadamard_rows 7168^2 (Hessian congruence)":
+            (lambda: encoder._hadamard(h, 1, su, per_col=True), 8 * k * k, "B"),
+        "hadamard_cols 7168^2 (Hessian congruence)":
+            (lambda: encoder._hadamard(h, 0, su, per_col=False), 8 * k * k, "B"),
+        "col_sumsq": (lambda: encoder._col_sumsq(w), 4 * k * n, "B"),
+        "block_ldl_normalize 7168": (lambda: encoder._lib.lib().qsrtb_block_ldl_normalize(
+            h.data_ptr(), k, k, None), 8 * k * k // 2, "B"),
+        "pack_trellis K3": (lambda: codec.pack_trellis_edges(states, bits), tiles * (512 + 32 * bits), "B"),
+        "unpack_decode K3 -> E4M3": (lambda: codec.decode_e4m3(packed, bits, lut), tiles * (32 * bits + 256), "B"),
+        "unpack K3 -> states": (lambda: codec.unpack_trellis_states(packed, bits), tiles * (32 * bits + 512), "B"),
+        "states_to_matrix": (lambda: codec.decode_regularized_weight(states, lut=lut), tiles * (512 + 1024), "B"),
+        "signed_block_hadamard rows 512": (lambda: coupled._transform_(w, 1, 512, signs_n, False), 8 * k * n, "B"),
+        "signed_block_hadamard cols 512": (lambda: coupled._transform_(w, 0, 512, signs_k, False), 16 * k * n, "B"),
+        f"weighted_syrk {args.rows}x{k}": (lambda: hessian.accumulate_hessian(acc, x, wts, accumulate=False),
+                                           args.rows * k * k, "F"),
+        "hessian_finish": (lambda: hessian.finish_hessian(acc, 1.0), 8 * k * k, "B"),
+    }
+    for name, (fn, work, kind) in cases.items():
+        if args.only and args.only not in name:
+            continue
+        ms = _time(fn, args.iters)
+        rate = work / (ms * 1e-3)
+        line = {"kernel": name, "ms": ms, "work_per_launch": work}
+        if kind == "B":
+            line["GB_per_s"] = rate / 1e9
+        else:
+            line["TFLOP_per_s"] = rate / 1e12
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -6,7 +6,8 @@
 // endian.  Both kernels therefore work on whole 32-bit words:
 //   pack   : 512 B of states in, 32*K B out per tile, one thread per output word;
 //   decode : 32*K B in, 512 B of states and/or 256 B of E4M3 labels out per tile.
-// Tiles are staged through shared memory so every global access is coalesced.
+// One warp handles one tile: a lane owns 8 consecutive symbols (one 16-byte load or store) and
+// exchanges bit chunks with its neighbours through warp shuffles; no shared memory.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -14,96 +15,126 @@
 
 namespace {
 
-constexpr int kPackTilesPerBlock = 16;
-constexpr int kPackThreads = 256;
+constexpr int kWarpsPerBlock = 8;  // one warp per tile, no shared memory, no block barriers
 
-__global__ void __launch_bounds__(kPackThreads)
+// A lane owns 8 consecutive symbols = 8*bits (16 / 24 / 32) bits of the tile's bitstream.
+__device__ __forceinline__ uint32_t lane_chunk(const uint4 v, int bits)
+{
+    const uint32_t mask = (1u << bits) - 1u;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t chunk = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        chunk = (chunk << bits) | (w[i] & mask);          // even symbol: low half-word
+        chunk = (chunk << bits) | ((w[i] >> 16) & mask);  // odd symbol: high half-word
+    }
+    return chunk;
+}
+
+__global__ void __launch_bounds__(32 * kWarpsPerBlock)
 pack_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, int bits,
             uint32_t* __restrict__ packed)
 {
-    __shared__ uint16_t sh[kPackTilesPerBlock * 256];
+    const int lane = threadIdx.x & 31;
+    const int chunk_bits = 8 * bits;
     const int words_per_tile = 8 * bits;
-    const uint32_t mask = (1u << bits) - 1u;
-    for (int64_t base = int64_t(blockIdx.x) * kPackTilesPerBlock; base < n_tiles;
-         base += int64_t(gridDim.x) * kPackTilesPerBlock) {
-        const int tiles_here = int(min(int64_t(kPackTilesPerBlock), n_tiles - base));
-        // 256 states = 512 B = 32 uint4 per tile
-        const uint4* src = reinterpret_cast<const uint4*>(states + base * 256);
-        for (int v = threadIdx.x; v < tiles_here * 32; v += kPackThreads)
-            reinterpret_cast<uint4*>(sh)[v] = src[v];
-        __syncthreads();
-        for (int wdx = threadIdx.x; wdx < tiles_here * words_per_tile; wdx += kPackThreads) {
-            const int tile = wdx / words_per_tile;
-            const int j = wdx - tile * words_per_tile;
-            const int bit0 = 32 * j;
-            const int s0 = bit0 / bits;
-            const int off = bit0 - s0 * bits;
-            const int count = (off + 32 + bits - 1) / bits;
-            const uint16_t* st = sh + tile * 256 + s0;
-            unsigned long long acc = 0;
-            for (int s = 0; s < count; ++s) acc = (acc << bits) | (st[s] & mask);
-            const int excess = count * bits - off - 32;
-            packed[(base + tile) * words_per_tile + j] = uint32_t(acc >> excess);
-        }
-        __syncthreads();
+    for (int64_t tile = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); tile < n_tiles;
+         tile += int64_t(gridDim.x) * kWarpsPerBlock) {
+        const uint4 v = reinterpret_cast<const uint4*>(states + tile * 256)[lane];
+        const uint32_t chunk = lane_chunk(v, bits);
+        // output word `lane` starts at bit 32*lane = chunk a, offset off inside chunks a, a+1
+        const int a = (32 * lane) / chunk_bits;
+        const int off = 32 * lane - a * chunk_bits;
+        const uint32_t ca = __shfl_sync(0xffffffffu, chunk, a & 31);
+        const uint32_t cb = __shfl_sync(0xffffffffu, chunk, (a + 1) & 31);
+        const unsigned long long both = (static_cast<unsigned long long>(ca) << chunk_bits) | cb;
+        const uint32_t word = uint32_t(both >> (2 * chunk_bits - off - 32));
+        if (lane < words_per_tile) packed[tile * words_per_tile + lane] = word;
     }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * kWarpsPerBlock)
 unpack_decode_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int bits,
                      const uint8_t* __restrict__ lut_state, uint16_t* __restrict__ out_states,
                      uint8_t* __restrict__ out_e4m3)
 {
-    __shared__ uint32_t words[33];
-    __shared__ uint16_t edges[256];
+    extern __shared__ __align__(16) uint8_t sh_lut[];  // 64 KiB copy of the table when decoding
+    if (out_e4m3) {
+        const uint4* src = reinterpret_cast<const uint4*>(lut_state);
+        for (int i = threadIdx.x; i < 4096; i += blockDim.x) reinterpret_cast<uint4*>(sh_lut)[i] = src[i];
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const int chunk_bits = 8 * bits;
     const int words_per_tile = 8 * bits;
-    const uint32_t mask = (1u << bits) - 1u;
-    const int lags = (16 + bits - 1) / bits;
-    const int i = threadIdx.x;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        if (i < words_per_tile) words[i] = packed[tile * words_per_tile + i];
-        if (i == words_per_tile) words[i] = 0;
-        __syncthreads();
-        const int bit0 = i * bits;
-        const int j = bit0 >> 5;
-        const int off = bit0 & 31;
-        const unsigned long long two = (static_cast<unsigned long long>(words[j]) << 32) | words[j + 1];
-        edges[i] = uint16_t((two >> (64 - off - bits)) & mask);
-        __syncthreads();
-        uint32_t state = 0;
-        for (int lag = 0; lag < lags; ++lag) state |= uint32_t(edges[(i - lag) & 255]) << (lag * bits);
-        state &= 0xffffu;
-        if (out_states) out_states[tile * 256 + i] = uint16_t(state);
-        if (out_e4m3) out_e4m3[tile * 256 + i] = lut_state[state];
-        __syncthreads();
+    const unsigned long long chunk_mask = (1ull << chunk_bits) - 1ull;
+    for (int64_t tile = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); tile < n_tiles;
+         tile += int64_t(gridDim.x) * kWarpsPerBlock) {
+        const uint32_t* words = packed + tile * words_per_tile;
+        const int bit0 = lane * chunk_bits;
+        const int w = bit0 >> 5, off = bit0 & 31;
+        const uint32_t w0 = words[w];
+        const uint32_t w1 = words[min(w + 1, words_per_tile - 1)];
+        const unsigned long long two = (static_cast<unsigned long long>(w0) << 32) | w1;
+        const uint32_t chunk = uint32_t((two >> (64 - off - chunk_bits)) & chunk_mask);
+        // the 8 symbols before this lane's (cyclic) complete every 16-bit state window
+        const uint32_t prev = __shfl_sync(0xffffffffu, chunk, (lane + 31) & 31);
+        const unsigned long long window = (static_cast<unsigned long long>(prev) << chunk_bits) | chunk;
+        uint32_t st[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) st[i] = uint32_t(window >> ((7 - i) * bits)) & 0xffffu;
+        if (out_states) {
+            const uint4 v = make_uint4(st[0] | (st[1] << 16), st[2] | (st[3] << 16),
+                                       st[4] | (st[5] << 16), st[6] | (st[7] << 16));
+            reinterpret_cast<uint4*>(out_states + tile * 256)[lane] = v;
+        }
+        if (out_e4m3) {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo |= uint32_t(sh_lut[st[i]]) << (8 * i);
+                hi |= uint32_t(sh_lut[st[4 + i]]) << (8 * i);
+            }
+            reinterpret_cast<uint2*>(out_e4m3 + tile * 256)[lane] = make_uint2(lo, hi);
+        }
     }
 }
 
 // states [kt, nt, 256] (tensor-core order) -> row-major float32 [kt*16, nt*16].
-// One block per tile; thread = row-major element, so the stores of a tile are 16 runs of 64 B.
-__global__ void __launch_bounds__(256)
+// One warp per tile.  Lane l holds tensor-core elements 8l..8l+7, i.e. rows {r0, r0+1, r0+8,
+// r0+9} x columns {c0, c0+8} with r0 = 2*(l%4), c0 = l/4 (exl3_encoder_backend.py:35-57): each
+// of its 8 stores lands in a run of 8 consecutive floats shared with 7 other lanes.
+__global__ void __launch_bounds__(32 * kWarpsPerBlock)
 states_to_matrix_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, int tiles_n,
                         const uint8_t* __restrict__ lut_state, float* __restrict__ out, int ld)
 {
-    __shared__ uint16_t sh[256];
-    const int e = threadIdx.x;  // row-major element: row = e / 16, col = e % 16
-    const int row = e >> 4, col = e & 15;
-    // position of (row, col) in tensor-core order (inverse of exl3_encoder_backend.py:35-57)
-    const int lane = ((col & 7) << 2) | ((row & 7) >> 1);
-    const int j = (row & 1) | ((row & 8) ? 2 : 0) | ((col & 8) ? 4 : 0);
-    const int src = lane * 8 + j;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        sh[e] = states[tile * 256 + e];
+    extern __shared__ __align__(16) uint8_t sh_lut[];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(lut_state);
+        for (int i = threadIdx.x; i < 4096; i += blockDim.x) reinterpret_cast<uint4*>(sh_lut)[i] = src[i];
         __syncthreads();
-        const uint8_t b = lut_state[sh[src]];
+    }
+    const int lane = threadIdx.x & 31;
+    const int r0 = (lane & 3) * 2, c0 = lane >> 2;
+    for (int64_t tile = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); tile < n_tiles;
+         tile += int64_t(gridDim.x) * kWarpsPerBlock) {
+        const uint4 v = reinterpret_cast<const uint4*>(states + tile * 256)[lane];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         const int64_t tk = tile / tiles_n;
         const int tn = int(tile - tk * tiles_n);
-        // E4M3 -> float: exact, via the bit pattern
-        const int ex = (b >> 3) & 15, m = b & 7;
-        float v = ex == 0 ? float(m) * 0.001953125f : __int_as_float(((ex + 120) << 23) | (m << 20));
-        if (b & 0x80) v = -v;
-        out[(tk * 16 + row) * int64_t(ld) + tn * 16 + col] = v;
-        __syncthreads();
+        float* base = out + (tk * 16) * int64_t(ld) + tn * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t state = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+            const uint8_t b = sh_lut[state];
+            // E4M3 -> float: exact, via the bit pattern
+            const int ex = (b >> 3) & 15, m = b & 7;
+            float value = ex == 0 ? float(m) * 0.001953125f : __int_as_float(((ex + 120) << 23) | (m << 20));
+            if (b & 0x80) value = -value;
+            const int row = r0 + (j & 1) + ((j & 2) ? 8 : 0);
+            const int col = c0 + ((j & 4) ? 8 : 0);
+            base[int64_t(row) * ld + col] = value;
+        }
     }
 }
 
@@ -116,6 +147,17 @@ int grid_for(int64_t blocks_wanted)
     return int(blocks_wanted < cap ? (blocks_wanted > 0 ? blocks_wanted : 1) : cap);
 }
 
+// Kernels that stage the 64 KiB table in shared memory run three blocks per SM and loop.
+int lut_grid(int64_t n_tiles)
+{
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int64_t wanted = (n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const int64_t cap = int64_t(sms) * 3;
+    return int(wanted < cap ? (wanted > 0 ? wanted : 1) : cap);
+}
+
 }  // namespace
 
 extern "C" int qsrtb_pack_trellis(const int16_t* states, int64_t n_tiles, int bits,
@@ -125,8 +167,8 @@ extern "C" int qsrtb_pack_trellis(const int16_t* states, int64_t n_tiles, int bi
     if (n_tiles < 0) return qsrtb_fail(QSRTB_EINVAL, "negative tile count");
     if (n_tiles == 0) return QSRTB_OK;
     if (!states || !packed) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
-    const int64_t blocks = (n_tiles + kPackTilesPerBlock - 1) / kPackTilesPerBlock;
-    pack_kernel<<<grid_for(blocks), kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    const int64_t blocks = (n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    pack_kernel<<<grid_for(blocks), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(states), n_tiles, bits, reinterpret_cast<uint32_t*>(packed));
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "pack launch");
@@ -142,7 +184,10 @@ extern "C" int qsrtb_unpack_decode(const int16_t* packed, int64_t n_tiles, int b
     if (n_tiles == 0) return QSRTB_OK;
     if (!packed || (!out_states && !out_e4m3)) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
     if (out_e4m3 && !lut_state) return qsrtb_fail(QSRTB_EINVAL, "decoding needs the table");
-    unpack_decode_kernel<<<grid_for(n_tiles), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const size_t smem = out_e4m3 ? 65536 : 0;
+    cudaFuncSetAttribute(unpack_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    const int grid = out_e4m3 ? lut_grid(n_tiles) : grid_for((n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    unpack_decode_kernel<<<grid, 32 * kWarpsPerBlock, smem, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint32_t*>(packed), n_tiles, bits, lut_state,
         reinterpret_cast<uint16_t*>(out_states), out_e4m3);
     const cudaError_t err = cudaGetLastError();
@@ -157,7 +202,8 @@ extern "C" int qsrtb_states_to_matrix(const int16_t* states, int tiles_k, int ti
     const int64_t n_tiles = int64_t(tiles_k) * tiles_n;
     if (n_tiles == 0) return QSRTB_OK;
     if (!states || !lut_state || !out) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
-    states_to_matrix_kernel<<<grid_for(n_tiles), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    cudaFuncSetAttribute(states_to_matrix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    states_to_matrix_kernel<<<lut_grid(n_tiles), 32 * kWarpsPerBlock, 65536, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(states), n_tiles, tiles_n, lut_state, out, ld);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "states_to_matrix launch");

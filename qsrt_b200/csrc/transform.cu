@@ -95,21 +95,30 @@ hadamard_rows_kernel(float* __restrict__ x, int batch, int rows, int cols, int l
 }
 
 // block = 128 threads = 128 columns; blockIdx.y = 128-row strip; blockIdx.z = matrix.
+// MODE: 0 no scaling, 1 scale inputs, 2 scale results; the scaling flavour is compiled in so
+// the unrolled 128-value strip carries no per-element branches.
+template <int MODE, bool PER_COL, bool DIVIDE>
 __global__ void __launch_bounds__(128)
-hadamard_cols_kernel(float* __restrict__ x, int rows, int cols, int ld, int64_t x_stride, ScaleSpec sc)
+hadamard_cols_kernel(float* __restrict__ x, int rows, int cols, int ld, int64_t x_stride,
+                     const float* __restrict__ scale, int64_t scale_stride)
 {
     const int c = blockIdx.x * 128 + threadIdx.x;
     if (c >= cols) return;
     const int r0 = blockIdx.y * 128;
     float* base = x + blockIdx.z * x_stride + int64_t(r0) * ld + c;
-    const float* vec = sc.vec ? sc.vec + blockIdx.z * sc.stride : nullptr;
-    const float col_s = (vec && sc.per_col) ? vec[c] : 1.0f;
+    const float* vec = MODE != 0 ? scale + blockIdx.z * scale_stride + (PER_COL ? c : r0) : nullptr;
+    float col_s = 1.0f;
+    if constexpr (MODE != 0 && PER_COL) col_s = vec[0];
+    auto scaled = [&](float value, int r) {
+        const float s = PER_COL ? col_s : vec[r];
+        return DIVIDE ? __fdiv_rn(value, s) : value * s;
+    };
     float v[128];
 #pragma unroll
     for (int r = 0; r < 128; ++r) v[r] = base[int64_t(r) * ld];
-    if (vec && !sc.after) {
+    if constexpr (MODE == 1) {
 #pragma unroll
-        for (int r = 0; r < 128; ++r) v[r] = apply_scale(v[r], sc.per_col ? col_s : vec[r0 + r], sc.divide);
+        for (int r = 0; r < 128; ++r) v[r] = scaled(v[r], r);
     }
 #pragma unroll
     for (int bit = 1; bit < 128; bit <<= 1) {
@@ -124,12 +133,25 @@ hadamard_cols_kernel(float* __restrict__ x, int rows, int cols, int ld, int64_t 
     }
 #pragma unroll
     for (int r = 0; r < 128; ++r) v[r] *= kInvSqrt128;
-    if (vec && sc.after) {
+    if constexpr (MODE == 2) {
 #pragma unroll
-        for (int r = 0; r < 128; ++r) v[r] = apply_scale(v[r], sc.per_col ? col_s : vec[r0 + r], sc.divide);
+        for (int r = 0; r < 128; ++r) v[r] = scaled(v[r], r);
     }
 #pragma unroll
     for (int r = 0; r < 128; ++r) base[int64_t(r) * ld] = v[r];
+}
+
+template <int MODE>
+void launch_hadamard_cols(dim3 grid, cudaStream_t s, float* x, int rows, int cols, int ld, int64_t x_stride,
+                          const ScaleSpec& sc)
+{
+    if (sc.per_col) {
+        if (sc.divide) hadamard_cols_kernel<MODE, true, true><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        else hadamard_cols_kernel<MODE, true, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+    } else {
+        if (sc.divide) hadamard_cols_kernel<MODE, false, true><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        else hadamard_cols_kernel<MODE, false, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+    }
 }
 
 // Column sums of squares: partial[chunk][col] over 256-row chunks, then a fixed-order fold.
@@ -252,7 +274,9 @@ extern "C" int qsrtb_hadamard128(float* x, int batch, int rows, int cols, int ld
                                                              row_sumsq, sumsq_stride);
     } else {
         dim3 grid((cols + 127) / 128, rows / 128, batch);
-        hadamard_cols_kernel<<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc);
+        if (!sc.vec) hadamard_cols_kernel<0, false, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, nullptr, 0);
+        else if (sc.after) launch_hadamard_cols<2>(grid, s, x, rows, cols, ld, x_stride, sc);
+        else launch_hadamard_cols<1>(grid, s, x, rows, cols, ld, x_stride, sc);
     }
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "hadamard launch");
