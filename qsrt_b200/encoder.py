@@ -710,7 +710,7 @@ def _side_streams(device: torch.device, count: int) -> list:
     return pool[:count]
 
 
-def ldlq_concurrent(jobs: list[tuple[torch.Tensor, torch.Tensor, dict]]):
+def ldlq_concurrent(jobs: list[tuple], max_streams: int = 4):
     """Run several independent stacked LDLQ recursions at once, each on its own stream.
 
     A 16-row step offers only ``batch * n / 16`` tiles; one persistent search launch then leaves
@@ -721,6 +721,11 @@ def ldlq_concurrent(jobs: list[tuple[torch.Tensor, torch.Tensor, dict]]):
 
     if not jobs:
         return []
+    if len(jobs) > max_streams:
+        done: list = []
+        for begin in range(0, len(jobs), max_streams):
+            done.extend(ldlq_concurrent(jobs[begin:begin + max_streams], max_streams))
+        return done
     device = jobs[0][0].device
     current = torch.cuda.current_stream(device)
     ready = torch.cuda.Event()
@@ -728,13 +733,16 @@ def ldlq_concurrent(jobs: list[tuple[torch.Tensor, torch.Tensor, dict]]):
     streams = _side_streams(device, len(jobs)) if len(jobs) > 1 else [current]
     outs: list[dict] = [{} for _ in jobs]
     gens = []
-    for (weights, Ls, quant_args), stream, out in zip(jobs, streams, outs):
-        stream.wait_event(ready)
+    for job, stream, out in zip(jobs, streams, outs):
+        weights, Ls, quant_args = job[:3]
+        plan = job[3] if len(job) > 3 else _uniform_plan(int(quant_args["K"]))
+        if stream is not current:
+            stream.wait_event(ready)
         with torch.cuda.stream(stream):
-            gens.append(_ldlq_steps(weights, Ls, quant_args, _uniform_plan(int(quant_args["K"])), out))
+            gens.append(_ldlq_steps(weights, Ls, quant_args, plan, out))
     alive = list(range(len(jobs)))
     # advance the longer recursions proportionally more often so that all finish together
-    lengths = [w.shape[1] // 16 for w, _, _ in jobs]
+    lengths = [job[0].shape[1] // 16 for job in jobs]
     progress = [0] * len(jobs)
     while alive:
         k = min(alive, key=lambda idx: (progress[idx] / lengths[idx], idx))
@@ -744,7 +752,8 @@ def ldlq_concurrent(jobs: list[tuple[torch.Tensor, torch.Tensor, dict]]):
                 progress[k] += 1
             except StopIteration:
                 alive.remove(k)
-    for stream, (weights, Ls, _), out in zip(streams, jobs, outs):
+    for stream, job, out in zip(streams, jobs, outs):
+        weights, Ls = job[0], job[1]
         if stream is not current:
             done = torch.cuda.Event()
             done.record(stream)
@@ -1084,4 +1093,124 @@ def _uniform_finish(state):
             qa.update({"apply_out_scales": apply_out_scales, "g_scale": state["g_scales"][t], "q_fallback": False})
             results[t] = (proxy_err, {"suh": suh, "svh": svh, "trellis": trellis})
         del Hd
+    return results
+
+
+def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_args_groups: list[list[dict]], *,
+                        return_weight_q: bool = True, verbose: bool = False):
+    """Prepare each source once and encode all of its mixed-rate candidates
+    (exl3_encoder_backend.py:3076-3394).
+
+    Per source: two-stage Hessian preparation with the complete conditioned ``su``, one
+    regularisation, one batched global-scale search; per candidate one BlockLDLQ recursion over
+    its tile-rate map (the candidates' recursions run concurrently on side streams).  Returns one
+    list per source of ``{"weight_q", "encoded", "suh", "svh", "proxy", "g_scale",
+    "h2_viterbi_refine"}``; the payload is not packed, as in the reference.  The reference's
+    candidate-reuse schedules (shared prefixes between candidates) are not reproduced: every
+    candidate is encoded in full, which yields the same kind of result at higher cost.
+    """
+
+    source_count = len(weights)
+    if source_count <= 0 or len(H_datas) != source_count or len(quant_args_groups) != source_count:
+        raise ValueError("QSRT batch inputs must have equal nonzero lengths")
+    if any(not group for group in quant_args_groups):
+        raise ValueError("every QSRT source needs at least one rate candidate")
+    if any(weight.ndim != 2 or weight.dtype != torch.float for weight in weights):
+        raise TypeError("QSRT batch weights must be float32 matrices")
+    shape = weights[0].shape
+    if any(weight.shape != shape for weight in weights):
+        raise ValueError("QSRT batch sources must have one matrix shape")
+    preparation_keys = (
+        "K", "seed", "sv_seed", "sigma_reg", "devices", "device_ratios", "apply_out_scales", "mcg", "mul1",
+        "shared_input_scales_key", "g_scale_into_sv", "buf_size_k", "ldlq_tf32", "tailbite_context",
+        "g_scale_override",
+    )
+    for group in quant_args_groups:
+        reference = group[0]
+        for args in group:
+            _reject_out_of_scope(args)
+            mixed_rate_spec(shape[0], shape[1], args)
+            for key in preparation_keys:
+                if args.get(key) != reference.get(key):
+                    raise ValueError(f"QSRT candidates changed preparation argument {key}")
+    devices = quant_args_groups[0][0]["devices"]
+    device = torch.device(devices[0])
+    if any(group[0].get("devices") != devices for group in quant_args_groups):
+        raise ValueError("QSRT source groups must share devices")
+    if any(weight.device != device for weight in weights):
+        raise ValueError("QSRT batch weights must already be on the quant device")
+
+    prepared = []
+    for weight, H_data, group in zip(weights, H_datas, quant_args_groups):
+        args = group[0]
+        q_fallback, _, su, H_diag = prepare_capture_H_for_conditioning(H_data, args, verbose)
+        if q_fallback:
+            raise ValueError("mixed-rate batching requires a non-fallback dense Hessian")
+        su = su.to(device)
+        sv = output_signs(weight.shape[1], device, args)
+        apply_out_scales, weight_r, _, su, sv = regularize(
+            weight, su, sv, args, verbose, H_diag.to(device) if H_diag is not None else None, None,
+            skip_g_scale=True, q_fallback=False,
+        )
+        q_fallback, H, L, su, _ = finalize_capture_H_with_conditioning(H_data, su, args, verbose)
+        if q_fallback or H is None or L is None:
+            raise ValueError("mixed-rate batching requires a non-fallback dense Hessian")
+        prepared.append({"H": H.to(device), "L": L.to(device), "weight_r": weight_r, "su": su.to(device),
+                         "sv": sv, "apply_out_scales": apply_out_scales})
+
+    scales: list = [None] * source_count
+    search_sources, search_samples = [], []
+    for source, (item, group) in enumerate(zip(prepared, quant_args_groups)):
+        override = group[0].get("g_scale_override")
+        if override is None:
+            search_sources.append(source)
+            search_samples.append(sample_scale_tiles(item["weight_r"]))
+        else:
+            if (isinstance(override, bool) or not isinstance(override, (int, float))
+                    or not math.isfinite(float(override)) or float(override) <= 0.0):
+                raise ValueError("g_scale_override must be positive and finite")
+            scales[source] = (float(override), None)
+    if search_samples:
+        searched = g_scale_search_batch(search_samples, quant_args_groups[search_sources[0]][0])
+        for source, result in zip(search_sources, searched):
+            scales[source] = result
+    for item, group, result in zip(prepared, quant_args_groups, scales):
+        g_scale, _ = result
+        item["weight_r"], item["su"], item["sv"] = apply_g_scale(
+            item["weight_r"], item["su"], item["sv"], g_scale, into_sv=bool(group[0].get("g_scale_into_sv")))
+        item["g_scale"] = g_scale
+
+    jobs, members = [], []
+    for source, group in enumerate(quant_args_groups):
+        item = prepared[source]
+        for candidate, args in enumerate(group):
+            plan = _mixed_plan(shape[0], shape[1], args, device)
+            jobs.append((item["weight_r"].unsqueeze(0), item["L"].unsqueeze(0), args, plan))
+            members.append((source, candidate))
+    encoded_all = ldlq_concurrent(jobs)
+
+    results: list[list[dict]] = [[] for _ in range(source_count)]
+    denominators = [block_trace(item["weight_r"], item["H"]) for item in prepared]
+    for (source, candidate), (weight_q, encoded) in zip(members, encoded_all):
+        item = prepared[source]
+        args = quant_args_groups[source][candidate]
+        weight_q, encoded = weight_q[0], encoded[0]
+        numerator = block_trace(item["weight_r"] - weight_q, item["H"])
+        if "suh" not in item:
+            item["suh"] = item["su"].flatten().contiguous().to(dtype=torch.half, copy=True)
+            item["svh"] = item["sv"].flatten().contiguous().to(dtype=torch.half, copy=True)
+        reconstruction = None
+        if return_weight_q:
+            reconstruction = _deregularize(weight_q, item["suh"].float(), item["svh"].float())
+        args.update({"apply_out_scales": item["apply_out_scales"], "g_scale": item["g_scale"], "q_fallback": False,
+                     "zeros": quant_args_groups[source][0].get("zeros", False)})
+        results[source].append({
+            "weight_q": reconstruction,
+            "encoded": encoded.contiguous(),
+            "suh": item["suh"],
+            "svh": item["svh"],
+            "proxy": numerator / max(denominators[source], 1e-8),
+            "g_scale": item["g_scale"],
+            "h2_viterbi_refine": {"enabled": False, "reason": "disabled", "sweeps": []},
+        })
     return results

@@ -250,3 +250,58 @@ class _CoupledSource(ExpertSource):
 
     execution: object = None
     activation: str = "silu"
+
+
+@dataclass
+class LayerSelection:
+    """Outcome of the mixed-rate candidate selection of one layer shard."""
+
+    bits: tuple[int, ...]                 # selected rate of every expert of the layer
+    table: torch.Tensor                   # [layer_experts, 3, 2] float64 (SSE, bytes), gathered
+    selected: dict                        # expert id -> ExpertPayload (local experts only)
+    total_sse: float
+    baseline_sse: float
+    exchanges: int
+    trellis_bpw: float
+
+
+def encode_layer_mixed(experts: list[ExpertSource], *, layer_experts: int, device: torch.device,
+                       budget_bpw: float = 3.083333, group=None, **encode_kwargs) -> LayerSelection:
+    """Mixed-rate candidate selection around a K3 baseline.
+
+    Every local expert is encoded completely at K2, K3 and K4; the routed functional error and
+    the payload size of each complete-expert candidate are all-gathered
+    (``selection.gather_candidate_table``, the path's only collective); every rank then runs the
+    same greedy equal-byte K2<->K4 exchange (``selection.equal_byte_exchange``) under the
+    trellis budget (3.083333 bpw = all-K3 plus one expert in twelve raised to K4); the selected
+    payloads are checked by decoding their packed bitstreams back to E4M3.
+    """
+
+    from . import selection
+
+    rates = (2, 3, 4)
+    device = torch.device(device)
+    by_rate = {b: encode_expert_batch(experts, bits=b, device=device, score=True, **encode_kwargs) for b in rates}
+    local_ids = [ex.expert_id for ex in experts]
+    local = torch.empty((len(experts), 3, 2), dtype=torch.float64, device=device)
+    for c, b in enumerate(rates):
+        for i, payload in enumerate(by_rate[b]):
+            trellis_bytes = sum(m.trellis.numel() * 2 for m in (payload.w1, payload.w3, payload.w2))
+            local[i, c, 0] = payload.routed_sse
+            local[i, c, 1] = float(trellis_bytes)
+    table = selection.gather_candidate_table(local, local_ids, layer_experts, group=group)
+    present = torch.isfinite(table[:, 1, 0])
+    if not bool(present.all()):
+        raise ValueError("the gathered candidate table does not cover every expert of the layer")
+    free_upgrades = int(round((budget_bpw - 3.0) * layer_experts + 1e-9))
+    allocation = selection.equal_byte_exchange(table, free_upgrades=max(0, free_upgrades))
+    chosen = {}
+    for i, ex in enumerate(experts):
+        payload = by_rate[allocation.bits[ex.expert_id]][i]
+        for matrix in (payload.w1, payload.w3, payload.w2):
+            if not verify_payload_roundtrip(matrix):
+                raise RuntimeError(f"expert {ex.expert_id}: packed payload failed its decode round trip")
+        chosen[ex.expert_id] = payload
+    k3_bytes = float(table[:, 1, 1].sum())
+    return LayerSelection(allocation.bits, table, chosen, allocation.total_sse, allocation.baseline_sse,
+                          allocation.exchanges, 3.0 * allocation.total_bytes / k3_bytes)

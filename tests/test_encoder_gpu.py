@@ -294,3 +294,43 @@ def test_mixed_rate_k_axis_matches_uniform_when_constant(cuda_device):
     enc = t2["trellis"].cpu().numpy()
     for col, b in enumerate(bits_map):
         assert oracle.states_close(enc[:, col], b)
+
+
+def test_quantize_qsrt_batch_candidates(cuda_device):
+    """Two sources, K2/K3/K4-mixed column maps per source: contract of the batch boundary
+    (qsrt/exl3_encoder_backend.py:3076-3394) and agreement with the single-matrix entry point."""
+
+    luts = {b: tables.sqg_xor_cheb_t12_bytes(b) for b in (2, 3, 4)}
+
+    def cand(bits_map):
+        a = _quant_args(3, cuda_device, g_scale_override=0.9)
+        del a["sqg_e4m3_lut"]
+        a.update({"sqg_e4m3_luts_by_bits": luts, "mixed_rate_axis": "n", "mixed_tile_bits": list(bits_map)})
+        return a
+
+    maps = ([3] * 16, [2] * 8 + [4] * 8)
+    weights, h_datas, groups = [], [], []
+    for e in range(2):
+        gate, hessian = _tiny_expert(1300 + e)
+        weights.append(gate.T.contiguous().to(cuda_device))
+        h_datas.append(encoder.make_shared_h(512, cuda_device, hessian))
+        groups.append([cand(m) for m in maps])
+    sources = [w.clone() for w in weights]
+    out = encoder.quantize_qsrt_batch(weights, h_datas, groups, return_weight_q=True)
+    assert len(out) == 2 and all(len(o) == 2 for o in out)
+    for src, res in zip(sources, out):
+        for bits_map, r in zip(maps, res):
+            assert r["encoded"].shape == (32, 16, 256) and r["encoded"].dtype == torch.int16
+            assert r["suh"].dtype == torch.float16 and r["svh"].shape == (256,)
+            enc = r["encoded"].cpu().numpy()
+            for col, b in enumerate(bits_map):
+                assert oracle.states_close(enc[:, col], b)
+            rel = float(((r["weight_q"] - src) ** 2).mean() / (src ** 2).mean())
+            assert rel < 0.2 and 0.0 < r["proxy"] < 1.0 and r["g_scale"] == 0.9
+        assert res[1]["proxy"] != res[0]["proxy"]
+    assert groups[0][0]["q_fallback"] is False and h_datas[0]["finalized"]
+    with pytest.raises(ValueError):
+        encoder.quantize_qsrt_batch(weights[:1], h_datas, groups)
+    bad = [cand(maps[0]), dict(cand(maps[1]), seed=99)]
+    with pytest.raises(ValueError):
+        encoder.quantize_qsrt_batch([sources[0].clone()], [encoder.make_shared_h(512, cuda_device)], [bad])

@@ -149,3 +149,28 @@ def test_coupled_coordinate_flow(cuda_device):
     out = execution.execute(ex.rows.float(), decoded, "silu")
     teacher = pipeline.gated_middle(ex.rows.float(), ex.w1, ex.w3, "silu") @ ex.w2.T
     assert float((out - teacher).norm() / teacher.norm()) < 0.35
+
+
+def test_mixed_rate_layer_selection(cuda_device):
+    """K2/K3/K4 candidates per expert, gathered table, equal-byte exchange, selected payloads
+    packed and decoded back to E4M3 bit-exactly (single process: the gather is the identity)."""
+
+    experts = _tiny_experts(cuda_device, count=4)
+    # make expert 1 insensitive (tiny gates) and expert 2 sensitive (large gates)
+    experts[1].gates = experts[1].gates * 0.05
+    experts[2].gates = experts[2].gates * 4.0
+    result = pipeline.encode_layer_mixed(experts, layer_experts=4, device=cuda_device, budget_bpw=3.0,
+                                         sigma_reg=1e-2)
+    assert result.table.shape == (4, 3, 2) and bool(torch.isfinite(result.table).all())
+    sse = result.table[:, :, 0]
+    assert bool((sse[:, 0] > sse[:, 1]).all()) and bool((sse[:, 1] > sse[:, 2]).all())
+    assert result.bits.count(2) == result.bits.count(4) == result.exchanges
+    assert result.total_sse <= result.baseline_sse
+    assert abs(result.trellis_bpw - 3.0) < 1e-9
+    if result.exchanges:
+        assert result.bits[2] == 4 and result.bits[1] == 2
+    for expert_id, payload in result.selected.items():
+        assert payload.bits == result.bits[expert_id]
+    raised = pipeline.encode_layer_mixed(experts[:2], layer_experts=2, device=cuda_device, budget_bpw=3.5,
+                                         sigma_reg=1e-2)
+    assert raised.bits.count(4) - raised.bits.count(2) == 1 and abs(raised.trellis_bpw - 3.5) < 1e-9
