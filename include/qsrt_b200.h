@@ -101,6 +101,18 @@ int qsrtb_hessian_accumulate(const float* rows, const float* weights, int64_t n_
                              int ld_rows, float* lower, int ld_h, int accumulate, void* stream);
 int qsrtb_hessian_finish(float* h, int d, int ld_h, double weight_sum, void* stream);
 
+/* Tensor-core variant of qsrtb_hessian_accumulate (same reference counterpart): tcgen05 TF32
+ * MMAs with the accumulator in tensor memory; the float32 inputs are split into TF32 head and
+ * tail (three products, float32 accumulation) so the result stays within 1e-5 of float64.
+ * Needs d % 128 == 0 and a workspace of qsrtb_hessian_tc_workspace_bytes(n_rows, d).
+ * *status_flag (device int, zeroed by the caller) becomes 1 if a bounded wait inside the kernel
+ * expired; the output is then undefined but the context stays usable.
+ */
+int qsrtb_hessian_tc_workspace_bytes(int64_t chunk_rows, int d, size_t* bytes);
+int qsrtb_hessian_accumulate_tc(const float* rows, const float* weights, int64_t n_rows, int d,
+                                int ld_rows, float* lower, int ld_h, int accumulate, void* workspace,
+                                size_t workspace_bytes, int* status_flag, void* stream);
+
 /* ---- R1 / H2 / D1: blockwise 128-point Hadamard with a fused sign/scale vector ----------
  * Replaces blockwise_preapply_had_l_/r_ and preapply_had_l/r together with the vector
  * scaling next to them (qsrt/exl3_encoder_backend.py:275-320, 2654-2675, 2142-2145,

@@ -40,6 +40,11 @@ _SIGNATURES = {
     "qsrtb_hessian_accumulate": (
         _c.c_int, [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR]
     ),
+    "qsrtb_hessian_tc_workspace_bytes": (_c.c_int, [_c.c_int64, _c.c_int, _c.POINTER(_c.c_size_t)]),
+    "qsrtb_hessian_accumulate_tc": (
+        _c.c_int,
+        [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR, _c.c_size_t, _PTR, _PTR],
+    ),
     "qsrtb_hessian_finish": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _c.c_double, _PTR]),
     "qsrtb_hadamard128": (
         _c.c_int,
@@ -71,6 +76,8 @@ _KERNELS_PER_CALL = {
     "qsrtb_last_error": 0,
     "qsrtb_viterbi_scratch_bytes": 0,
     "qsrtb_viterbi_set_units": 0,
+    "qsrtb_hessian_tc_workspace_bytes": 0,
+    "qsrtb_hessian_accumulate_tc": 2,
     "qsrtb_col_sumsq": 2,
     "qsrtb_block_ldl_normalize": 2,
     "qsrtb_signed_block_hadamard": 1,

@@ -89,6 +89,8 @@ def main() -> None:
         "signed_block_hadamard cols 512": (lambda: coupled._transform_(w, 0, 512, signs_k, False), 16 * k * n, "B"),
         f"weighted_syrk {args.rows}x{k}": (lambda: hessian.accumulate_hessian(acc, x, wts, accumulate=False),
                                            args.rows * k * k, "F"),
+        f"weighted_syrk tcgen05 3xTF32 {args.rows}x{k}": (
+            lambda: hessian.accumulate_hessian_tensor_cores(acc, x, wts, accumulate=False), args.rows * k * k, "F"),
         "hessian_finish": (lambda: hessian.finish_hessian(acc, 1.0), 8 * k * k, "B"),
     }
     for name, (fn, work, kind) in cases.items():

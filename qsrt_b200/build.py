@@ -18,6 +18,21 @@ NVCC_FLAGS = [
 ]
 
 
+def cutlass_include() -> Path | None:
+    """CUTLASS / CuTe header tree used by the tcgen05 kernels (vendored inside site-packages)."""
+
+    import importlib.util
+
+    for package, relative in (("flashinfer", "data/cutlass/include"), ("tilelang", "3rdparty/cutlass/include")):
+        spec = importlib.util.find_spec(package)
+        if spec is None or not spec.submodule_search_locations:
+            continue
+        candidate = Path(list(spec.submodule_search_locations)[0]) / relative
+        if (candidate / "cute" / "arch" / "mma_sm100_umma.hpp").exists():
+            return candidate
+    return None
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -39,10 +54,14 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     build_dir = PACKAGE / "build"
     build_dir.mkdir(exist_ok=True)
     procs = []
+    cutlass = cutlass_include()
+    extra = ["-I", str(cutlass)] if cutlass is not None else ["-DQSRTB_NO_CUTLASS"]
     for src in sources():
         obj = build_dir / (src.stem + ".o")
         objects.append(obj)
         cmd = ["nvcc", *NVCC_FLAGS, "-I", str(PACKAGE.parent / "include"), "-c", str(src), "-o", str(obj)]
+        if src.name.endswith("_tc.cu"):
+            cmd[1:1] = extra
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -17,6 +17,56 @@ from . import _lib
 from .tiles import _stream_ptr
 
 
+# Rows handed to one tensor-core launch (its split operands take 24 bytes per row and feature).
+TENSOR_CORE_CHUNK_ROWS = 2048
+_tc_workspace: dict[str, torch.Tensor] = {}
+
+
+def accumulate_hessian_tensor_cores(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *,
+                                    accumulate: bool = True) -> None:
+    """``lower (+)= sum_r w_r x_r x_r^T`` with tcgen05 TF32 MMAs (split operands, float32
+    accumulation in tensor memory).  The feature count must be a multiple of 128."""
+
+    import ctypes
+
+    d = lower.shape[0]
+    if lower.ndim != 2 or lower.shape[1] != d or lower.dtype != torch.float32 or not lower.is_cuda or not lower.is_contiguous():
+        raise ValueError("the accumulator must be a contiguous square CUDA float32 matrix")
+    if d % 128:
+        raise ValueError("the tensor-core Hessian needs a feature count that is a multiple of 128")
+    rows = rows.to(device=lower.device, dtype=torch.float32).contiguous()
+    if rows.ndim != 2 or rows.shape[1] != d:
+        raise ValueError("invalid covariance sample shapes")
+    if weights is not None:
+        weights = weights.to(device=lower.device, dtype=torch.float32).contiguous()
+    device = lower.device
+    wanted = ctypes.c_size_t(0)
+    _lib.check(_lib.lib().qsrtb_hessian_tc_workspace_bytes(TENSOR_CORE_CHUNK_ROWS, d, ctypes.byref(wanted)),
+               "qsrtb_hessian_tc_workspace_bytes")
+    key = str(device)
+    work = _tc_workspace.get(key)
+    if work is None or work.numel() < wanted.value:
+        work = torch.empty(wanted.value, dtype=torch.uint8, device=device)
+        _tc_workspace[key] = work
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    first = not accumulate
+    with torch.cuda.device(device):
+        for begin in range(0, rows.shape[0], TENSOR_CORE_CHUNK_ROWS):
+            chunk = rows[begin:begin + TENSOR_CORE_CHUNK_ROWS]
+            w = weights[begin:begin + TENSOR_CORE_CHUNK_ROWS] if weights is not None else None
+            _lib.check(
+                _lib.lib().qsrtb_hessian_accumulate_tc(
+                    chunk.data_ptr(), w.data_ptr() if w is not None else None, chunk.shape[0], d, d,
+                    lower.data_ptr(), d, 0 if first else 1, work.data_ptr(), work.numel(), status.data_ptr(),
+                    _stream_ptr(device),
+                ),
+                "qsrtb_hessian_accumulate_tc",
+            )
+            first = False
+    if int(status.item()) != 0:
+        raise RuntimeError("tensor-core Hessian kernel gave up waiting for its MMAs (status flag set)")
+
+
 def accumulate_hessian(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *, accumulate: bool = True) -> None:
     """``lower (+)= sum_r w_r x_r x_r^T`` on the lower triangle of a CUDA float32 matrix."""
 
@@ -55,7 +105,8 @@ def finish_hessian(lower: torch.Tensor, weight_sum: float) -> torch.Tensor:
 
 
 def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: torch.device,
-                        chunk_rows: int = 65536, return_cpu: bool = True) -> tuple[torch.Tensor, float]:
+                        chunk_rows: int = 65536, return_cpu: bool = True,
+                        tensor_cores: bool = False) -> tuple[torch.Tensor, float]:
     """Return ``sum(w * x xT) / sum(w)`` as symmetric FP32 (qsrt/candidate_hessian.py:70-112).
 
     ``chunk_rows`` only bounds the staging copy of host-resident rows; the kernel streams any
@@ -81,8 +132,10 @@ def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: to
         raise ValueError("covariance weights must have a positive finite sum")
     accumulator = torch.empty((dimension, dimension), dtype=torch.float32, device=device)
     first = True
+    use_tc = bool(tensor_cores) and dimension % 128 == 0
     for begin in range(0, int(rows.shape[0]), chunk_rows):
-        accumulate_hessian(accumulator, rows[begin:begin + chunk_rows], weights[begin:begin + chunk_rows], accumulate=not first)
+        step = accumulate_hessian_tensor_cores if use_tc else accumulate_hessian
+        step(accumulator, rows[begin:begin + chunk_rows], weights[begin:begin + chunk_rows], accumulate=not first)
         first = False
     covariance = finish_hessian(accumulator, denominator)
     if return_cpu:

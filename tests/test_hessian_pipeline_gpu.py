@@ -174,3 +174,19 @@ def test_mixed_rate_layer_selection(cuda_device):
     raised = pipeline.encode_layer_mixed(experts[:2], layer_experts=2, device=cuda_device, budget_bpw=3.5,
                                          sigma_reg=1e-2)
     assert raised.bits.count(4) - raised.bits.count(2) == 1 and abs(raised.trellis_bpw - 3.5) < 1e-9
+
+
+@pytest.mark.parametrize("rows,dim", [(300, 128), (1365, 512), (2500, 1024)])
+def test_tensor_core_hessian_within_1e5_of_fp64(cuda_device, rows, dim):
+    """tcgen05 TF32 path with split operands: same 1e-5 relative Frobenius bar as the SIMT path."""
+
+    g = torch.Generator().manual_seed(rows * 7 + dim)
+    x = torch.randn((rows, dim), generator=g) * torch.exp(0.5 * torch.randn(dim, generator=g))
+    w = torch.rand(rows, generator=g).square()
+    got, _ = hessian.weighted_covariance(x, w, device=cuda_device, tensor_cores=True)
+    x64 = x.double()
+    ref = (x64.T * w.double()) @ x64 / w.double().sum()
+    assert _rel_fro(got, ref) < 1e-5
+    assert torch.equal(got, got.T)
+    simt, _ = hessian.weighted_covariance(x, w, device=cuda_device)
+    assert _rel_fro(got, simt) < 1e-5
