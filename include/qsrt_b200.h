@@ -184,6 +184,42 @@ int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier
 int qsrtb_pack_trellis(const int16_t* states, int64_t n_tiles, int bits, int16_t* packed,
                        void* stream);
 
+/* ---- P2: mixed-rate record container and atom-major storage image ------------------------
+ * Replaces pack_qsrt_trellis / unpack_qsrt_trellis_edges / unpack_qsrt_trellis_states
+ * (qsrt/qsrt.py:1051-1172) and, with layout 1, pack_matrix_atoms + rotate_expert_atoms written
+ * straight into a layer image (qsrt/qsrt_storage.py:194-231,347-362,441-462).
+ *
+ * states [tiles_k, tiles_n, 256] int16.  The rate axis (0 = K/rows, 1 = N/columns) is cut into
+ * n_records records of `stripes` tiles; record r is stored with record_bits[r] (HOST array) bits
+ * per edge.  layout 0: records back to back, tiles of a record in row-major tile order (the
+ * reference's one-dimensional payload).  layout 1: atom (pair p, stripe s) = stripe s of record
+ * 2p then stripe s of record 2p+1, stored at dst + ((p*stripes + s + rotation) mod n_atoms) *
+ * atom_pitch_bytes; rotation and atom_pitch_bytes are ignored for layout 0.
+ * open_paths (device int, may be NULL): incremented once per tile whose states are not the
+ * closed cyclic walk of their own low bits (the reference raises ValueError for such input).
+ */
+int qsrtb_pack_records(const int16_t* states, int tiles_k, int tiles_n, int rate_axis,
+                       int n_records, int stripes, const uint8_t* record_bits, int layout,
+                       int rotation, int64_t atom_pitch_bytes, int16_t* dst, int64_t dst_bytes,
+                       int* open_paths, void* stream);
+
+/* Inverse of qsrtb_pack_records: 16-bit cyclic states and/or the stored K-bit edge symbols, each
+ * [tiles_k, tiles_n, 256] int16 (either may be NULL).
+ */
+int qsrtb_unpack_records(const int16_t* src, int64_t src_bytes, int tiles_k, int tiles_n,
+                         int rate_axis, int n_records, int stripes, const uint8_t* record_bits,
+                         int layout, int rotation, int64_t atom_pitch_bytes, int16_t* out_states,
+                         int16_t* out_edges, void* stream);
+
+/* Moves complete packed tile paths between the record payload and the atom layout without
+ * decoding a bit (pack_matrix_atoms / unpack_matrix_atoms, qsrt/qsrt_storage.py:194-289).
+ * to_records = 0: records -> atoms; 1: atoms -> records.
+ */
+int qsrtb_records_atoms(int16_t* records, int64_t records_bytes, int tiles_k, int tiles_n,
+                        int rate_axis, int n_records, int stripes, const uint8_t* record_bits,
+                        int rotation, int64_t atom_pitch_bytes, int16_t* atoms, int64_t atoms_bytes,
+                        int to_records, void* stream);
+
 /* ---- D1: decoder -------------------------------------------------------------------------
  * Replaces unpack_trellis_states + LUT decode (qsrt/qsrt.py:886-913,
  * qsrt/exl3_reference.py:34-83).  packed [n_tiles, 16*bits] -> states [n_tiles,256] int16

@@ -61,6 +61,21 @@ _SIGNATURES = {
     ),
     "qsrtb_block_ldl_normalize": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _PTR]),
     "qsrtb_pack_trellis": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR]),
+    "qsrtb_pack_records": (
+        _c.c_int,
+        [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _c.c_int64,
+         _PTR, _c.c_int64, _PTR, _PTR],
+    ),
+    "qsrtb_unpack_records": (
+        _c.c_int,
+        [_PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int,
+         _c.c_int64, _PTR, _PTR, _PTR],
+    ),
+    "qsrtb_records_atoms": (
+        _c.c_int,
+        [_PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int64,
+         _PTR, _c.c_int64, _c.c_int, _PTR],
+    ),
     "qsrtb_states_to_matrix": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _PTR, _PTR, _c.c_int, _PTR]),
     "qsrtb_unpack_decode": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR, _PTR, _PTR]),
 }

@@ -15,7 +15,7 @@ import json
 
 import torch
 
-from . import codec, coupled, encoder, hessian, tables
+from . import codec, coupled, encoder, hessian, records, storage, tables
 
 
 _flush = None
@@ -69,7 +69,53 @@ def main() -> None:
     signs_n = torch.ones(n, device=dev)
     signs_k = torch.ones(k, device=dev)
 
+    # record container / atom image: 16 Kimi-geometry matrices per timed call (350 MB of states)
+    rec_states = [codec.reconstruct_trellis_states(
+        torch.randint(0, 4, (192, 224, 256), device=dev, dtype=torch.int16, generator=g), 2) for _ in range(16)]
+    rec_bytes = 16 * (192 * 224 * (512 + 96))
+    layout = storage.QSRTLayerLayout(16, 880)
+    image = torch.zeros(layout.disk_bytes, dtype=torch.uint8, device=dev)
+    scale = torch.ones(3072, dtype=torch.float16, device=dev)
+    rec_payloads = [records.pack_qsrt_trellis(s_, "K2", rate_axis="k") for s_ in rec_states]
+
+    rec_states_n = [s_.reshape(224, 192, 256) for s_ in rec_states]   # same tiles, N-axis geometry
+
+    def write_image():
+        for slot in range(5):
+            trio = {"w1": rec_states_n[3 * slot], "w3": rec_states_n[3 * slot + 1], "w2": rec_states[3 * slot + 2]}
+            storage.write_expert_atoms(image, layout, 9, slot, slot, trio, {"w1": 0, "w3": 0, "w2": 0},
+                                       {"w1": scale, "w3": scale, "w2": scale}, validate_states=False)
+
+    # one large launch of the same kernels: 64 records x 32 stripes along K, 224 tiles across
+    big_bits = records._bits_array(tuple((2, 4, 3, 3)[r % 4] for r in range(64)))
+    big_k, big_n = 64 * 32, 224
+    big_states = torch.randint(-32768, 32767, (big_k, big_n, 256), device=dev, dtype=torch.int16, generator=g)
+    big_payload = torch.empty(big_k * big_n * 48, dtype=torch.int16, device=dev)
+    big_pitch = 224 * 32 * 6
+    lib = encoder._lib.lib()
+
+    def big_pack(layout_id):
+        encoder._lib.check(lib.qsrtb_pack_records(
+            big_states.data_ptr(), big_k, big_n, 0, 64, 32, big_bits, layout_id, 5 if layout_id else 0,
+            big_pitch if layout_id else 0, big_payload.data_ptr(), big_payload.numel() * 2, None, None), "pack")
+
+    def big_unpack():
+        encoder._lib.check(lib.qsrtb_unpack_records(
+            big_payload.data_ptr(), big_payload.numel() * 2, big_k, big_n, 0, 64, 32, big_bits, 0, 0, 0,
+            big_states.data_ptr(), None, None), "unpack")
+
+    big_tiles = big_k * big_n
     cases = {
+        "pack_records kernel, record layout (458k tiles, mixed K2/K3/K4)": (lambda: big_pack(0), big_tiles * (512 + 96), "B"),
+        "pack_records kernel, atom layout (458k tiles)": (lambda: big_pack(1), big_tiles * (512 + 96), "B"),
+        "unpack_records kernel -> states (458k tiles)": (big_unpack, big_tiles * (512 + 96), "B"),
+        "pack_records R2 (16 matrices)":
+            (lambda: [records.pack_qsrt_trellis(s_, "R2", rate_axis="k", validate_states=False) for s_ in rec_states],
+             rec_bytes, "B"),
+        "unpack_records K2 -> states (16 matrices)":
+            (lambda: [records.unpack_qsrt_trellis_states(p_) for p_ in rec_payloads],
+             16 * 192 * 224 * (64 + 512), "B"),
+        "write_expert_atoms R0 (5 experts -> layer image)": (write_image, 15 * 192 * 224 * (512 + 96), "B"),
         "hadamard_rows (divide by sv + had_r + row sums)":
             (lambda: encoder._hadamard(w, 1, sv, per_col=True, divide=True, row_sumsq=sums), 8 * k * n, "B"),
         "hadamard_cols (divide by su + had_l)":

@@ -97,3 +97,38 @@ def coupled_inputs(hidden: int = 512, inter: int = 128, rows: int = 48, seed: in
     m = torch.randn((rows, inter), generator=g)
     h2 = (m.T @ m / rows).float()
     return w1, w3, w2, x, h13, h2
+
+
+# ---- mixed-rate record container / atom storage cases (Kimi-K3 geometry, the only one the
+# reference container accepts) ----------------------------------------------------------------
+RECORD_CASES = tuple((mode, axis) for mode in ("R0", "R1", "R2", "H308", "K2") for axis in ("k", "n"))
+EXPERT_CASE = (9, 77, 1, 2)  # layer, expert, r13 (w1/w3 mode), r2 (w2 mode)
+_MODE_IDS = {"R0": 0, "R1": 1, "R2": 2, "H308": 3, "K2": 4}
+
+
+def record_shape(axis: str) -> tuple[int, int, int]:
+    return (192, 224, 256) if axis == "k" else (224, 192, 256)
+
+
+def record_case_seed(mode: str, axis: str) -> int:
+    return 200 + 10 * _MODE_IDS[mode] + (axis == "n")
+
+
+def expert_case_inputs():
+    """Seeded numpy states, local (3072) and shared (3584) float16 scales of one expert."""
+
+    import numpy as np
+
+    from oracle.records_oracle import legal_states
+
+    _, _, r13, r2 = EXPERT_CASE
+    bits_of = {0: (3,) * 24, 1: (2, 4) + (3,) * 22, 2: (2, 4, 2, 4) + (3,) * 20}
+    rng = np.random.default_rng(4242)
+    states, local, shared = {}, {}, {}
+    for index, matrix in enumerate(("w1", "w3", "w2")):
+        axis = "k" if matrix == "w2" else "n"
+        bits = bits_of[r2 if matrix == "w2" else r13]
+        states[matrix] = legal_states(record_shape(axis), bits, axis, 900 + index)
+        local[matrix] = (rng.standard_normal(3072) * 0.1).astype(np.float16)
+        shared[matrix] = (rng.standard_normal(3584) * 0.1).astype(np.float16)
+    return states, local, shared
