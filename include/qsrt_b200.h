@@ -176,6 +176,22 @@ int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier
                              int tile_map_count, void* scratch, size_t scratch_bytes,
                              void* stream);
 
+/* Same step for an arbitrary set of live encoder states that share source matrices: the
+ * continuation form of ldlq_mixed_batched (qsrt/exl3_encoder_backend.py:1190-1478, its
+ * `source_indices` argument) used by the candidate prefix trie (:1645-1830).  members is a DEVICE
+ * array of member_count (source, owner) int32 pairs: visited matrix b reads rows of source matrix
+ * members[2b] of w and reads/writes matrix members[2b+1] of comp / wq / err / out_states.  All
+ * other arguments as qsrtb_ldlq_quantize_rows.
+ */
+int qsrtb_ldlq_quantize_members(const float* w, const float* comp, float multiplier,
+                                const int32_t* members, int member_count, int n, int ld,
+                                int comp_ld, int64_t w_stride, int64_t comp_stride,
+                                const uint8_t* lut_state, const uint8_t* lut_pm, int bits,
+                                int tailbite_context, int variant, float* wq, float* err,
+                                int16_t* out_states, int64_t state_stride,
+                                const int32_t* tile_map, int tile_map_count, void* scratch,
+                                size_t scratch_bytes, void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).

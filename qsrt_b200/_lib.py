@@ -37,6 +37,12 @@ _SIGNATURES = {
          _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_int64, _PTR, _c.c_int,
          _PTR, _c.c_size_t, _PTR],
     ),
+    "qsrtb_ldlq_quantize_members": (
+        _c.c_int,
+        [_PTR, _PTR, _c.c_float, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,
+         _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_int64, _PTR, _c.c_int,
+         _PTR, _c.c_size_t, _PTR],
+    ),
     "qsrtb_hessian_accumulate": (
         _c.c_int, [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR]
     ),

@@ -475,6 +475,8 @@ struct TileIO {
     int comp_ld;          // row pitch of comp
     int tiles_n;          // column tiles visited per matrix
     const int* tile_map;  // optional: visited column tile i is tile_map[i] (mixed-rate maps)
+    const int2* members;  // optional: visited matrix b reads source matrix members[b].x of w and
+                          // owns matrix members[b].y of comp / wq / err / out_states
     float multiplier;
     int rows_mode;
 };
@@ -527,24 +529,32 @@ viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
     }
 
     // Offsets are recomputed after the search rather than kept live across it (registers).
-    auto locate = [&](int64_t tile, int64_t& w_off, int64_t& comp_off, int64_t& state_off) {
+    auto locate = [&](int64_t tile, int64_t& src_off, int64_t& w_off, int64_t& comp_off, int64_t& state_off) {
         const int64_t b = tile / io.tiles_n;
         int tn = int(tile - b * io.tiles_n);
         if (io.tile_map != nullptr) tn = io.tile_map[tn];
+        int64_t source = b, owner = b;
+        if (io.members != nullptr) {
+            const int2 m = io.members[b];
+            source = m.x;
+            owner = m.y;
+        }
         int col;
         const int row = tensor_core_rc(threadIdx.x, col);
-        w_off = b * io.w_stride + int64_t(row) * io.ld + tn * 16 + col;
-        comp_off = b * io.comp_stride + int64_t(row) * io.comp_ld + tn * 16 + col;
-        state_off = b * io.state_stride + int64_t(tn) * 256 + threadIdx.x;
+        const int64_t inside = int64_t(row) * io.ld + tn * 16 + col;
+        src_off = source * io.w_stride + inside;
+        w_off = owner * io.w_stride + inside;
+        comp_off = owner * io.comp_stride + int64_t(row) * io.comp_ld + tn * 16 + col;
+        state_off = owner * io.state_stride + int64_t(tn) * 256 + threadIdx.x;
     };
 
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         if (threadIdx.x < 256) {
             float w;
             if (io.rows_mode) {
-                int64_t w_off, comp_off, state_off;
-                locate(tile, w_off, comp_off, state_off);
-                w = io.w[w_off];
+                int64_t src_off, w_off, comp_off, state_off;
+                locate(tile, src_off, w_off, comp_off, state_off);
+                w = io.w[src_off];
                 if (io.comp != nullptr && io.multiplier != 0.0f) {
                     const float c = io.comp[comp_off];
                     w = (io.multiplier == 1.0f) ? __fadd_rn(w, c) : __fadd_rn(w, __fmul_rn(io.multiplier, c));
@@ -566,11 +576,11 @@ viterbi_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
             const uint16_t s = sm->states[threadIdx.x];
             const float q = e4m3_to_float(lut_state[s]);
             if (io.rows_mode) {
-                int64_t w_off, comp_off, state_off;
-                locate(tile, w_off, comp_off, state_off);
+                int64_t src_off, w_off, comp_off, state_off;
+                locate(tile, src_off, w_off, comp_off, state_off);
                 io.out_states[state_off] = s;
                 io.wq[w_off] = q;
-                if (io.err != nullptr) io.err[w_off] = __fsub_rn(io.w[w_off], q);
+                if (io.err != nullptr) io.err[w_off] = __fsub_rn(io.w[src_off], q);
             } else {
                 io.out_states[tile * 256 + threadIdx.x] = s;
                 io.out_tiles[tile * 256 + threadIdx.x] = q;
@@ -726,14 +736,13 @@ extern "C" int qsrtb_quantize_tiles(const float* tiles, int64_t n_tiles, const u
                     scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier,
-                                        int batch, int n, int ld, int comp_ld, int64_t w_stride,
-                                        int64_t comp_stride, const uint8_t* lut_state,
-                                        const uint8_t* lut_pm, int bits, int tailbite_context,
-                                        int variant, float* wq, float* err, int16_t* out_states,
-                                        int64_t state_stride, const int32_t* tile_map,
-                                        int tile_map_count, void* scratch, size_t scratch_bytes,
-                                        void* stream)
+namespace {
+int quantize_rows_impl(const float* w, const float* comp, float multiplier, int batch, int n, int ld,
+                       int comp_ld, int64_t w_stride, int64_t comp_stride, const uint8_t* lut_state,
+                       const uint8_t* lut_pm, int bits, int tailbite_context, int variant, float* wq,
+                       float* err, int16_t* out_states, int64_t state_stride, const int32_t* tile_map,
+                       int tile_map_count, const int32_t* members, void* scratch, size_t scratch_bytes,
+                       void* stream)
 {
     if (batch < 0 || n < 0 || (n % 16) != 0) return qsrtb_fail(QSRTB_EINVAL, "n must be a multiple of 16");
     if (tile_map && (tile_map_count < 0 || tile_map_count > n / 16))
@@ -748,6 +757,8 @@ extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float
     if (ld < n || (comp && comp_ld < n)) return qsrtb_fail(QSRTB_EINVAL, "row pitch smaller than n");
     if (!(multiplier >= 0.0f && multiplier <= 1.0f))
         return qsrtb_fail(QSRTB_EINVAL, "ldlq feedback multiplier must be in [0, 1]");
+    if (members && (reinterpret_cast<uintptr_t>(members) & 7))
+        return qsrtb_fail(QSRTB_EINVAL, "member table must be 8-byte aligned");
     TileIO io{};
     io.w = w;
     io.comp = comp;
@@ -761,10 +772,41 @@ extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float
     io.comp_ld = comp_ld;
     io.tiles_n = visited;
     io.tile_map = tile_map;
+    io.members = reinterpret_cast<const int2*>(members);
     io.multiplier = multiplier;
     io.rows_mode = 1;
     return dispatch(io, n_tiles, lut_state, lut_pm, bits, tailbite_context, variant, scratch,
                     scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int qsrtb_ldlq_quantize_rows(const float* w, const float* comp, float multiplier,
+                                        int batch, int n, int ld, int comp_ld, int64_t w_stride,
+                                        int64_t comp_stride, const uint8_t* lut_state,
+                                        const uint8_t* lut_pm, int bits, int tailbite_context,
+                                        int variant, float* wq, float* err, int16_t* out_states,
+                                        int64_t state_stride, const int32_t* tile_map,
+                                        int tile_map_count, void* scratch, size_t scratch_bytes,
+                                        void* stream)
+{
+    return quantize_rows_impl(w, comp, multiplier, batch, n, ld, comp_ld, w_stride, comp_stride, lut_state,
+                              lut_pm, bits, tailbite_context, variant, wq, err, out_states, state_stride,
+                              tile_map, tile_map_count, nullptr, scratch, scratch_bytes, stream);
+}
+
+extern "C" int qsrtb_ldlq_quantize_members(const float* w, const float* comp, float multiplier,
+                                           const int32_t* members, int member_count, int n, int ld,
+                                           int comp_ld, int64_t w_stride, int64_t comp_stride,
+                                           const uint8_t* lut_state, const uint8_t* lut_pm, int bits,
+                                           int tailbite_context, int variant, float* wq, float* err,
+                                           int16_t* out_states, int64_t state_stride,
+                                           const int32_t* tile_map, int tile_map_count, void* scratch,
+                                           size_t scratch_bytes, void* stream)
+{
+    if (!members) return qsrtb_fail(QSRTB_EINVAL, "member table required");
+    return quantize_rows_impl(w, comp, multiplier, member_count, n, ld, comp_ld, w_stride, comp_stride,
+                              lut_state, lut_pm, bits, tailbite_context, variant, wq, err, out_states,
+                              state_stride, tile_map, tile_map_count, members, scratch, scratch_bytes, stream);
 }
 
 // Tuning knob (not part of the reference interface): units per thread, 1 or 2.

@@ -1214,3 +1214,11 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
             "h2_viterbi_refine": {"enabled": False, "reason": "disabled", "sweeps": []},
         })
     return results
+
+
+# candidate-grid entry points of the quantizer module (defined in their own file)
+from .candidates import (  # noqa: E402
+    ldlq_mixed_batched,
+    ldlq_mixed_k_candidates_prefix_reuse,
+    ldlq_mixed_n_candidates_reuse,
+)
