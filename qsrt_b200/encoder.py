@@ -1102,12 +1102,13 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
     (exl3_encoder_backend.py:3076-3394).
 
     Per source: two-stage Hessian preparation with the complete conditioned ``su``, one
-    regularisation, one batched global-scale search; per candidate one BlockLDLQ recursion over
-    its tile-rate map (the candidates' recursions run concurrently on side streams).  Returns one
+    regularisation, one batched global-scale search; then the candidates' BlockLDLQ recursions over
+    their tile-rate maps, batched.  Returns one
     list per source of ``{"weight_q", "encoded", "suh", "svh", "proxy", "g_scale",
-    "h2_viterbi_refine"}``; the payload is not packed, as in the reference.  The reference's
-    candidate-reuse schedules (shared prefixes between candidates) are not reproduced: every
-    candidate is encoded in full, which yields the same kind of result at higher cost.
+    "h2_viterbi_refine"}``; the payload is not packed, as in the reference.  Candidates are encoded
+    through the reference's reuse schedules where their maps allow it (``:3245-3293``): shared
+    K3 columns once for output-axis maps over an all-K3 first candidate, the shared backwards
+    prefix once for input-axis maps, a plain batch over shared sources otherwise.
     """
 
     source_count = len(weights)
@@ -1180,14 +1181,23 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
             item["weight_r"], item["su"], item["sv"], g_scale, into_sv=bool(group[0].get("g_scale_into_sv")))
         item["g_scale"] = g_scale
 
-    jobs, members = [], []
-    for source, group in enumerate(quant_args_groups):
-        item = prepared[source]
-        for candidate, args in enumerate(group):
-            plan = _mixed_plan(shape[0], shape[1], args, device)
-            jobs.append((item["weight_r"].unsqueeze(0), item["L"].unsqueeze(0), args, plan))
-            members.append((source, candidate))
-    encoded_all = ldlq_concurrent(jobs)
+    members = [(source, candidate) for source, group in enumerate(quant_args_groups) for candidate in range(len(group))]
+    axes = [[mixed_rate_spec(shape[0], shape[1], args) for args in group] for group in quant_args_groups]
+    source_weights = torch.stack([item["weight_r"] for item in prepared])
+    source_Ls = torch.stack([item["L"] for item in prepared])
+    if all(all(axis == "n" for axis, _ in group) and group[0][1] == (3,) * (shape[1] // 16) for group in axes):
+        # output-axis maps over an all-K3 first candidate: encode the shared columns once
+        weights_q, encoded_q = ldlq_mixed_n_candidates_reuse(source_weights, source_Ls, quant_args_groups)
+    elif any(len(group) > 1 for group in axes) and all(all(axis == "k" for axis, _ in group) for group in axes):
+        # input-axis maps: encode the rows the candidates agree on once, then a trie of states
+        weights_q, encoded_q = ldlq_mixed_k_candidates_prefix_reuse(source_weights, source_Ls, quant_args_groups)
+    else:
+        weights_q, encoded_q = ldlq_mixed_batched(
+            source_weights, source_Ls, [quant_args_groups[s][c] for s, c in members],
+            source_indices=torch.tensor([s for s, _ in members], dtype=torch.long, device=device),
+        )
+    del source_Ls
+    encoded_all = [(weights_q[i:i + 1], encoded_q[i:i + 1]) for i in range(len(members))]
 
     results: list[list[dict]] = [[] for _ in range(source_count)]
     denominators = [block_trace(item["weight_r"], item["H"]) for item in prepared]
