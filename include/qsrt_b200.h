@@ -192,6 +192,16 @@ int qsrtb_ldlq_quantize_members(const float* w, const float* comp, float multipl
                                 const int32_t* tile_map, int tile_map_count, void* scratch,
                                 size_t scratch_bytes, void* stream);
 
+/* ---- source ingest: MXFP4 expert weights -> float32 ------------------------------------------
+ * Replaces dequant (qsrt/io/mxfp4.py:50-63; unpack_codes :19-30, scale_factors :42-44,
+ * code_values :45-48) and the transpose into encoder orientation that follows it.
+ * packed uint8 [out_rows, in_cols/2] (low nibble = even input), scale uint8 [out_rows, in_cols/32]
+ * (E8M0, 2^(byte-127)).  transposed = 0: dst [out_rows, in_cols]; 1: dst [in_cols, out_rows].
+ * Bit-exact with the reference's float32 arithmetic.
+ */
+int qsrtb_mxfp4_dequant(const uint8_t* packed, const uint8_t* scale, int out_rows, int in_cols,
+                        float* dst, int ld, int transposed, void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).

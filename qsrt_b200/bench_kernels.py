@@ -15,7 +15,7 @@ import json
 
 import torch
 
-from . import codec, coupled, encoder, hessian, records, storage, tables
+from . import codec, coupled, encoder, hessian, mxfp4, records, storage, tables
 
 
 _flush = None
@@ -105,7 +105,14 @@ def main() -> None:
             big_states.data_ptr(), None, None), "unpack")
 
     big_tiles = big_k * big_n
+    mx_rows, mx_cols = 8192, 7168   # four gate-shaped source matrices
+    mx_packed = torch.randint(0, 256, (mx_rows, mx_cols // 2), device=dev, dtype=torch.uint8, generator=g)
+    mx_scale = torch.randint(110, 130, (mx_rows, mx_cols // 32), device=dev, dtype=torch.uint8, generator=g)
+    mx_bytes = mx_rows * mx_cols * 4 + mx_packed.numel() + mx_scale.numel()
     cases = {
+        "mxfp4_dequant [out, in]": (lambda: mxfp4.dequant(mx_packed, mx_scale), mx_bytes, "B"),
+        "mxfp4_dequant -> encoder orientation [in, out]":
+            (lambda: mxfp4.dequant_encoder_orientation(mx_packed, mx_scale), mx_bytes, "B"),
         "pack_records kernel, record layout (458k tiles, mixed K2/K3/K4)": (lambda: big_pack(0), big_tiles * (512 + 96), "B"),
         "pack_records kernel, atom layout (458k tiles)": (lambda: big_pack(1), big_tiles * (512 + 96), "B"),
         "unpack_records kernel -> states (458k tiles)": (big_unpack, big_tiles * (512 + 96), "B"),

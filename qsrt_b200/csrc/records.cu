@@ -44,22 +44,22 @@ struct Placement {
 };
 
 // q-th tile in destination order
-__device__ __forceinline__ Placement place(const RecordLayout& g, int64_t q)
+__device__ __forceinline__ Placement place(const RecordLayout& g, int q)
 {
     Placement p;
     int record, stripe, o;
     if (g.layout == 0) {
-        const int64_t per_record = int64_t(g.stripes) * g.orth;
-        record = int(q / per_record);
-        const int idx = int(q - record * per_record);
+        const int per_record = g.stripes * g.orth;
+        record = q / per_record;
+        const int idx = q - record * per_record;
         if (g.rate_axis == 0) { stripe = idx / g.orth; o = idx - stripe * g.orth; }
         else                  { o = idx / g.stripes;   stripe = idx - o * g.stripes; }
         p.bits = g.bits[record];
         p.dst32 = g.record_off32[record] + int64_t(idx) * 8 * p.bits;
     } else {
         const int per_atom = 2 * g.orth;
-        const int atom = int(q / per_atom);
-        const int rem = int(q - int64_t(atom) * per_atom);
+        const int atom = q / per_atom;
+        const int rem = q - atom * per_atom;
         const int side = rem / g.orth;
         o = rem - side * g.orth;
         const int pair = atom / g.stripes;
@@ -105,7 +105,7 @@ pack_records_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, Record
     const int lane = threadIdx.x & 31;
     for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
          q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement p = place(g, q);
+        const Placement p = place(g, int(q));
         const int chunk_bits = 8 * p.bits;
         const uint4 v = reinterpret_cast<const uint4*>(states + p.src_tile * 256)[lane];
         const uint32_t chunk = lane_chunk(v, p.bits);
@@ -137,7 +137,7 @@ unpack_records_kernel(const uint32_t* __restrict__ src, int64_t n_tiles, RecordL
     const int lane = threadIdx.x & 31;
     for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
          q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement p = place(g, q);
+        const Placement p = place(g, int(q));
         const int chunk_bits = 8 * p.bits;
         const uint32_t* words = src + p.dst32;
         const int bit0 = lane * chunk_bits;
@@ -172,7 +172,7 @@ records_atoms_kernel(uint32_t* __restrict__ records, int64_t n_tiles, RecordLayo
     const int lane = threadIdx.x & 31;
     for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
          q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement pa = place(g_atoms, q);
+        const Placement pa = place(g_atoms, int(q));
         // the same source tile's position in record order
         const int tk = int(pa.src_tile / g_atoms.tiles_n), tn = int(pa.src_tile - int64_t(tk) * g_atoms.tiles_n);
         const int along = g_atoms.rate_axis == 0 ? tk : tn, o = g_atoms.rate_axis == 0 ? tn : tk;
@@ -202,6 +202,7 @@ int make_layout(int tiles_k, int tiles_n, int rate_axis, int n_records, int stri
                 RecordLayout* g, int64_t* extent_bytes)
 {
     if (tiles_k <= 0 || tiles_n <= 0) return qsrtb_fail(QSRTB_EINVAL, "tile grid must be positive");
+    if (int64_t(tiles_k) * tiles_n > (int64_t(1) << 30)) return qsrtb_fail(QSRTB_EINVAL, "tile grid too large");
     if (rate_axis != 0 && rate_axis != 1) return qsrtb_fail(QSRTB_EINVAL, "rate_axis must be 0 (k) or 1 (n)");
     if (n_records <= 0 || n_records > kMaxRecords || stripes <= 0 || !record_bits)
         return qsrtb_fail(QSRTB_EINVAL, "bad record description");
