@@ -383,7 +383,12 @@ def run_b200(args) -> None:
             "peak": peak,
             "unit": "G branch metrics/s",
             "frac": achieved / peak if peak > 0 else None,
-            "traffic": None,
+            # DRAM bytes per launch: one ncu capture of this kernel on 592 tiles measured
+            # 1 104.7 MB read + written = 1.866 MB per tile (the survivor rows); the traffic grows
+            # in proportion to the tiles, so it is scaled to this run's average launch.
+            "traffic": NCU_DRAM_BYTES_PER_TILE * search_tiles / max(search_launches, 1),
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 592-tile launch, scaled per tile",
+            "algorithmic_dram_bytes_per_tile": 4 * 256 * 4 + 256 * 2,  # rows + compensation in, reconstruction + error + states out
             "peak_source": "live half2 FMA probe / 3 half ops per branch metric (MEASURED_PEAKS.json holds no ALU figure)",
             "launches": search_launches,
             "avg_launch_ms": launch_ms_sum / max(search_launches, 1),
@@ -433,6 +438,9 @@ def cpu_tile_baseline(payload) -> dict:
         "sample": f"{n} K3 tiles (tailbite context 128) of this workload through the C restatement of the tile "
                   f"search only, OpenMP on {cores} threads, {dt:.1f} s",
     }
+
+
+NCU_DRAM_BYTES_PER_TILE = (817.1e6 + 287.6e6) / 592
 
 
 def main() -> None:
