@@ -1,24 +1,35 @@
 // Calibration Hessian on the 5th-generation tensor cores:  C (+)= sum_r w_r x_r x_r^T  as a
-// tcgen05 (UMMA) TF32 contraction with the accumulator in tensor memory.
+// TMA-fed, warp-specialised tcgen05 (UMMA) TF32 contraction with the accumulators in tensor memory.
 //
 // Precision: one TF32 pass would give ~1e-4 relative error; the float32 inputs are therefore
-// split into a TF32 head and a TF32 tail (x = hi + lo, exactly) and the three significant
-// products hi*hi + lo*hi + hi*lo are accumulated in float32.  The split is folded into the
-// contraction dimension: with A' = [hi(x) | lo(x) | hi(x)] and B' = [hi(wx) | hi(wx) | lo(wx)]
-// (both feature-major, K-major operands) a single GEMM over K' = 3R does all three products.
+// split exactly into a TF32 head and a TF32 tail (x = hi + lo) and the three significant
+// products hi*hi + lo*hi + hi*lo are accumulated in float32.  The tensor core adds each 8-deep
+// product group to its float32 accumulator with truncation; over thousands of groups that bias
+// alone exceeds 1e-5, so the contraction is cut into segments of 60 instruction groups whose
+// partial sums leave tensor memory and are added up in round-to-nearest float32 registers.
 //
-//   prepare kernel : transposes a chunk of rows into A' and B' (shared-memory tile transpose,
-//                    coalesced on both sides), applies the row weight and the split.
-//   gemm kernel    : one CTA per lower-triangular 128x128 tile of C.  Per 32-wide K block the
-//                    CTA stages 2 x 16 KiB operand tiles in 128-byte-swizzled shared memory
-//                    (double buffered), one elected thread issues four 128x128x8
-//                    tcgen05.mma.kind::tf32 instructions and commits them to an mbarrier; the
-//                    128 x 128 float accumulator lives in 128 TMEM columns and is read back
-//                    once with tcgen05.ld for the epilogue.
-// Every mbarrier wait is bounded; on expiry the kernel raises a status flag, releases its
-// tensor memory and returns.
+//   prepare kernel : transposes a chunk of rows into four K-major planes [d, r_pad]:
+//                    hi(x), lo(x), hi(w x), lo(w x)  (shared-memory tile transpose).
+//   gemm kernel    : one CTA (6 warps) per lower-triangular 128x128 tile of C.
+//       warp 0     : TMA producer.  Per step of 32 rows it brings four 128x32 operand tiles
+//                    (16 KiB each, 128-byte swizzle) into one of three shared-memory stages
+//                    with cp.async.bulk.tensor and arms the stage's "full" mbarrier.
+//       warp 1     : MMA issuer.  The warp waits for the stage, one elected lane issues twelve 128x128x8
+//                    tcgen05.mma.kind::tf32 (hi*whi, lo*whi, hi*wlo for four 8-deep blocks) and
+//                    commits them to the stage's "empty" mbarrier; after a segment it commits to
+//                    the accumulator's "ready" mbarrier and moves to the other accumulator.
+//       warps 2..5 : epilogue.  Each warp owns 32 rows of the tile: it waits for "ready", reads its
+//                    lanes of the 128-column accumulator with tcgen05.ld, adds them to 128
+//                    float32 registers and arrives on the accumulator's "free" mbarrier; at the
+//                    end it writes (or adds) its rows of C.
+// The two 128-column accumulators let segment s+1 run on the tensor core while segment s is read
+// out.  No multicast and no clusters: every tile comes from this GPU's own memory.
+// Every mbarrier wait is bounded; on expiry the kernel raises a status flag, lets its copies
+// land, releases its tensor memory and returns.
 //
-// Built on the CuTe sm100 atoms (cute/arch/mma_sm100_umma.hpp, tmem_allocator_sm100.hpp).
+// MMA atoms, shared-memory layouts and matrix descriptors come from the CuTe sm100 headers
+// (cute/arch/mma_sm100_umma.hpp, tmem_allocator_sm100.hpp); TMA, mbarrier and tcgen05.ld are
+// inline PTX.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -26,10 +37,11 @@
 
 #if !defined(QSRTB_NO_CUTLASS)
 
+#include <cuda.h>
+
 #include <cute/tensor.hpp>
 #include <cute/arch/cluster_sm90.hpp>
 #include <cute/arch/tmem_allocator_sm100.hpp>
-#include <cute/algorithm/cooperative_copy.hpp>
 #include <cutlass/arch/barrier.h>
 #include <cutlass/numeric_types.h>
 
@@ -37,11 +49,13 @@ namespace qsrtb_tc {
 
 using namespace cute;
 
-constexpr int kTile = 128;   // output tile edge
-constexpr int kBlockK = 32;  // contraction elements per staged block (one 128-byte swizzle row)
-constexpr int kThreads = 128;
-constexpr int kWaitLimit = 4000000;
-constexpr int kSegmentTiles = 16;  // 512 contraction elements per tensor-memory accumulation
+constexpr int kTile = 128;      // output tile edge
+constexpr int kBlockK = 32;     // contraction elements per stage (one 128-byte swizzle row)
+constexpr int kStages = 3;
+constexpr int kThreads = 192;   // producer warp, MMA warp, four epilogue warps
+constexpr long long kWaitCycles = 40000000;   // about 20 ms: far beyond any healthy wait
+constexpr int kSegmentSteps = 5;   // 5 steps x 12 instructions = 60 accumulations per segment
+constexpr int kTileBytes = kTile * kBlockK * 4;
 
 using Element = cutlass::tfloat32_t;
 
@@ -52,10 +66,10 @@ __device__ __forceinline__ float tf32_round(float x)
     return __uint_as_float(u & 0xffffe000u);
 }
 
-// rows [R, d] (row pitch ld) -> a_split, b_split [d, 3 * r_pad] (K-major)
+// rows [R, d] (row pitch ld) -> planes[4][d][r_pad]: hi(x), lo(x), hi(wx), lo(wx)
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ rows, const float* __restrict__ weights, int64_t n_rows,
-                       int d, int ld, int r_pad, float* __restrict__ a_split, float* __restrict__ b_split)
+                       int d, int ld, int r_pad, float* __restrict__ planes)
 {
     __shared__ float tile[32][33];
     __shared__ float wts[32];
@@ -68,7 +82,7 @@ split_transpose_kernel(const float* __restrict__ rows, const float* __restrict__
         tile[ty + 8 * i][tx] = (r < n_rows && c < d) ? rows[int64_t(r) * ld + c] : 0.0f;
     }
     __syncthreads();
-    const int64_t pitch = 3 * int64_t(r_pad);
+    const int64_t plane = int64_t(d) * r_pad;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int c = c0 + ty + 8 * i;   // feature
@@ -76,28 +90,40 @@ split_transpose_kernel(const float* __restrict__ rows, const float* __restrict__
         if (c >= d || r >= r_pad) continue;
         const float x = tile[tx][ty + 8 * i];
         const float wx = x * wts[tx];
-        const float x_hi = tf32_round(x), x_lo = tf32_round(x - x_hi);
-        const float w_hi = tf32_round(wx), w_lo = tf32_round(wx - w_hi);
-        float* a = a_split + int64_t(c) * pitch + r;
-        float* b = b_split + int64_t(c) * pitch + r;
-        a[0] = x_hi;         b[0] = w_hi;
-        a[r_pad] = x_lo;     b[r_pad] = w_hi;
-        a[2 * r_pad] = x_hi; b[2 * r_pad] = w_lo;
+        const float x_hi = tf32_round(x), w_hi = tf32_round(wx);
+        float* out = planes + int64_t(c) * r_pad + r;
+        out[0] = x_hi;
+        out[plane] = tf32_round(x - x_hi);
+        out[2 * plane] = w_hi;
+        out[3 * plane] = tf32_round(wx - w_hi);
     }
 }
 
-template <class ASmemLayout, class BSmemLayout>
-struct SharedStorage {
-    alignas(128) cute::ArrayEngine<Element, cute::cosize_v<ASmemLayout>> A[2];
-    alignas(128) cute::ArrayEngine<Element, cute::cosize_v<BSmemLayout>> B[2];
-    alignas(16) cute::uint64_t mma_barrier[2];
-    alignas(16) cute::uint32_t tmem_base_ptr;
+struct Maps {
+    CUtensorMap plane[4];
 };
 
-__device__ __forceinline__ bool bounded_wait(uint64_t* barrier, uint32_t phase)
+template <class SmemLayout>
+struct SharedStorage {
+    // operand kinds: 0 = hi(x), 1 = lo(x) (rows of tile bi); 2 = hi(wx), 3 = lo(wx) (rows of bj)
+    alignas(1024) cute::ArrayEngine<Element, cute::cosize_v<SmemLayout>> operand[4];
+    alignas(16) uint64_t full[kStages];
+    alignas(16) uint64_t empty[kStages];
+    alignas(16) uint64_t ready[2];
+    alignas(16) uint64_t free_[2];
+    uint32_t tmem_base_ptr;
+    volatile int failed;
+    volatile uint32_t first_failure;
+};
+
+// Waits for a phase of an mbarrier for at most kWaitCycles; `where` identifies the wait in the
+// status word the host reads (role in the top byte, barrier index below, sequence number low).
+template <class Storage>
+__device__ __forceinline__ bool bounded_wait(Storage& shared, uint64_t* barrier, uint32_t phase, uint32_t where)
 {
     const uint32_t addr = cute::cast_smem_ptr_to_uint(barrier);
-    for (int i = 0; i < kWaitLimit; ++i) {
+    const long long start = clock64();
+    for (int i = 0;; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -105,37 +131,51 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* barrier, uint32_t phase)
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(addr), "r"(phase) : "memory");
         if (done) return true;
+        if (shared.failed) return false;   // another role already gave up
+        if ((i & 15) == 15 && clock64() - start > kWaitCycles) break;
     }
+    if (atomicCAS(const_cast<int*>(&shared.failed), 0, int(where)) == 0) shared.first_failure = where;
     return false;
 }
 
-// Copy one 128 x 32 operand block (row pitch k_total) into its swizzled shared-memory tile with
-// 16-byte accesses: the 128-byte swizzle permutes whole 16-byte chunks, so four consecutive
-// contraction elements stay contiguous.  Tile coordinates are ((row, k % 8), 0, k / 8).
-template <class SmemTensor>
-__device__ __forceinline__ void stage_tile(const Element* __restrict__ base, int tile_row, int k_tile,
-                                           int k_total, SmemTensor& smem)
+__device__ __forceinline__ void arrive(uint64_t* barrier)
 {
-    const Element* src = base + int64_t(tile_row) * kTile * k_total + int64_t(k_tile) * kBlockK;
-#pragma unroll
-    for (int i = 0; i < (kTile * kBlockK / 4) / kThreads; ++i) {
-        const int chunk = threadIdx.x + i * kThreads;   // 8 chunks of 16 bytes per row
-        const int row = chunk >> 3, k4 = (chunk & 7) * 4;
-        const uint4 v = *reinterpret_cast<const uint4*>(src + int64_t(row) * k_total + k4);
-        Element* dst = &smem(make_coord(make_coord(row, k4 & 7), 0, k4 >> 3));
-        *reinterpret_cast<uint4*>(dst) = v;
-    }
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(cute::cast_smem_ptr_to_uint(barrier)) : "memory");
 }
 
-template <class TiledMMA, class ASmemLayout, class BSmemLayout>
-__global__ void __launch_bounds__(128, 1)
-syrk_tcgen05_kernel(const Element* __restrict__ a_ptr, const Element* __restrict__ b_ptr, int d, int k_total,
-                    float* __restrict__ c_ptr, int ldc, int accumulate, int* __restrict__ status,
-                    TiledMMA tiled_mma, ASmemLayout, BSmemLayout)
+// One 128 x 32 float tile: element column x (a multiple of 32, i.e. 128 bytes), row y.
+__device__ __forceinline__ void tma_load_tile(const CUtensorMap* map, void* smem_dst, uint64_t* barrier, int x, int y)
 {
-    extern __shared__ __align__(128) char smem_raw[];
-    using Storage = SharedStorage<ASmemLayout, BSmemLayout>;
-    Storage& shared = *reinterpret_cast<Storage*>(smem_raw);
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(cute::cast_smem_ptr_to_uint(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
+           "r"(cute::cast_smem_ptr_to_uint(barrier))
+        : "memory");
+}
+
+// 16 consecutive accumulator columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16])
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <class TiledMMA, class SmemLayout>
+__global__ void __launch_bounds__(kThreads, 1)
+syrk_tcgen05_kernel(const __grid_constant__ Maps maps, int d, int k_steps, float* __restrict__ c_ptr, int ldc,
+                    int accumulate, int* __restrict__ status, TiledMMA tiled_mma, SmemLayout)
+{
+    extern __shared__ __align__(1024) char smem_raw[];
+    using Storage = SharedStorage<SmemLayout>;
+    Storage& shared = *reinterpret_cast<Storage*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     // lower-triangular tile pair of this CTA
     int bi = int((sqrtf(8.0f * float(blockIdx.x) + 1.0f) - 1.0f) * 0.5f);
@@ -143,122 +183,156 @@ syrk_tcgen05_kernel(const Element* __restrict__ a_ptr, const Element* __restrict
     while (bi * (bi + 1) / 2 > int(blockIdx.x)) --bi;
     const int bj = int(blockIdx.x) - bi * (bi + 1) / 2;
 
-    Tensor mA = make_tensor(make_gmem_ptr(a_ptr), make_shape(d, k_total), make_stride(k_total, _1{}));
-    Tensor mB = make_tensor(make_gmem_ptr(b_ptr), make_shape(d, k_total), make_stride(k_total, _1{}));
-    Tensor mC = make_tensor(make_gmem_ptr(c_ptr), make_shape(d, d), make_stride(ldc, _1{}));
-    Tensor gA = local_tile(mA, Shape<Int<kTile>, Int<kBlockK>>{}, make_coord(bi, _));  // (128, 32, k_tiles)
-    Tensor gB = local_tile(mB, Shape<Int<kTile>, Int<kBlockK>>{}, make_coord(bj, _));
-    Tensor gC = local_tile(mC, Shape<Int<kTile>, Int<kTile>>{}, make_coord(bi, bj));    // (128, 128)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // shared-memory operand views (MmaAtom, NumMma_M, NumMma_K, stage) and their descriptors
     ThrMMA cta_mma = tiled_mma.get_slice(0);
-    Tensor tCgA = cta_mma.partition_A(gA);   // (MmaA, NumMma_M, NumMma_K, k_tiles)
-    Tensor tCgB = cta_mma.partition_B(gB);
-    Tensor tCgC = cta_mma.partition_C(gC);   // (MmaC, NumMma_M, NumMma_N)
+    Tensor sXhi = make_tensor(make_smem_ptr(shared.operand[0].begin()), SmemLayout{});
+    Tensor sXlo = make_tensor(make_smem_ptr(shared.operand[1].begin()), SmemLayout{});
+    Tensor sWhi = make_tensor(make_smem_ptr(shared.operand[2].begin()), SmemLayout{});
+    Tensor sWlo = make_tensor(make_smem_ptr(shared.operand[3].begin()), SmemLayout{});
+    Tensor dXhi = cta_mma.make_fragment_A(sXhi);
+    Tensor dXlo = cta_mma.make_fragment_A(sXlo);
+    Tensor dWhi = cta_mma.make_fragment_B(sWhi);
+    Tensor dWlo = cta_mma.make_fragment_B(sWlo);
 
-    Tensor tCsA0 = make_tensor(make_smem_ptr(shared.A[0].begin()), ASmemLayout{});
-    Tensor tCsA1 = make_tensor(make_smem_ptr(shared.A[1].begin()), ASmemLayout{});
-    Tensor tCsB0 = make_tensor(make_smem_ptr(shared.B[0].begin()), BSmemLayout{});
-    Tensor tCsB1 = make_tensor(make_smem_ptr(shared.B[1].begin()), BSmemLayout{});
-    Tensor tCrA0 = cta_mma.make_fragment_A(tCsA0);   // shared-memory matrix descriptors
-    Tensor tCrA1 = cta_mma.make_fragment_A(tCsA1);
-    Tensor tCrB0 = cta_mma.make_fragment_B(tCsB0);
-    Tensor tCrB1 = cta_mma.make_fragment_B(tCsB1);
-    Tensor tCtAcc = cta_mma.make_fragment_C(tCgC);   // tensor-memory accumulator
+    Tensor mC = make_tensor(make_gmem_ptr(c_ptr), make_shape(d, d), make_stride(ldc, _1{}));
+    Tensor gC = local_tile(mC, Shape<Int<kTile>, Int<kTile>>{}, make_coord(bi, bj));
+    Tensor tCgC = cta_mma.partition_C(gC);
+    Tensor tCtAcc0 = cta_mma.make_fragment_C(tCgC);   // tensor-memory accumulators
+    Tensor tCtAcc1 = cta_mma.make_fragment_C(tCgC);
 
-    const uint32_t elect_one_warp = (threadIdx.x / 32 == 0);
     using TmemAllocator = cute::TMEM::Allocator1Sm;
     TmemAllocator tmem_allocator{};
-    if (elect_one_warp) tmem_allocator.allocate(kTile, &shared.tmem_base_ptr);
-    if (threadIdx.x == 0) {
-        cute::initialize_barrier(shared.mma_barrier[0], 1);
-        cute::initialize_barrier(shared.mma_barrier[1], 1);
+    if (warp == 0) tmem_allocator.allocate(2 * kTile, &shared.tmem_base_ptr);
+    if (threadIdx.x == 32) {
+        for (int s = 0; s < kStages; ++s) {
+            cute::initialize_barrier(shared.full[s], 1);
+            cute::initialize_barrier(shared.empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            cute::initialize_barrier(shared.ready[a], 1);
+            cute::initialize_barrier(shared.free_[a], 4 * 32);
+        }
+        shared.failed = 0;
+        shared.first_failure = 0;
+        cutlass::arch::fence_barrier_init();
     }
     __syncthreads();
-    tCtAcc.data() = shared.tmem_base_ptr;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = shared.tmem_base_ptr;
+    tCtAcc0.data() = tmem_base;
+    tCtAcc1.data() = tmem_base + kTile;
 
-    const int k_tiles = size<3>(tCgA);
-    bool ok = true;
-    uint32_t phase[2] = {0, 0};
+    const int segments = (k_steps + kSegmentSteps - 1) / kSegmentSteps;
 
-    TiledCopy tiled_t2r = make_tmem_copy(SM100_TMEM_LOAD_32dp32b1x{}, tCtAcc);
-    ThrCopy thr_t2r = tiled_t2r.get_slice(threadIdx.x);
-    Tensor tDtAcc = thr_t2r.partition_S(tCtAcc);
-    Tensor tDgC = thr_t2r.partition_D(tCgC);
-
-    // The tensor core adds each 8-deep product group to the float32 accumulator with
-    // truncation; over thousands of groups that bias exceeds 1e-5.  The contraction is therefore
-    // cut into segments of kSegmentTiles blocks whose partial sums are added to C in ordinary
-    // round-to-nearest float32.
-    for (int seg_begin = 0; seg_begin < k_tiles && ok; seg_begin += kSegmentTiles) {
-        const int seg_end = min(k_tiles, seg_begin + kSegmentTiles);
-        tiled_mma.accumulate_ = UMMA::ScaleOut::Zero;
-        for (int k_tile = seg_begin; k_tile < seg_end; ++k_tile) {
-            const int buf = k_tile & 1;
-            // the buffer was last read by the MMAs of k_tile - 2: wait for their commit
-            if (k_tile - seg_begin >= 2) {
-                // block-uniform verdict, so that no thread is left behind at a barrier
-                ok = __syncthreads_and(bounded_wait(&shared.mma_barrier[buf], phase[buf]));
-                phase[buf] ^= 1;
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int kt = 0; kt < k_steps && ok; ++kt) {
+                const int s = kt % kStages;
+                if (kt >= kStages) ok = bounded_wait(shared, &shared.empty[s], uint32_t((kt / kStages - 1) & 1), 0x01000000u | uint32_t(kt));
                 if (!ok) break;
+                cute::set_barrier_transaction_bytes(shared.full[s], 4 * kTileBytes);
+                const int x = kt * kBlockK;
+                tma_load_tile(&maps.plane[0], shared.operand[0].begin() + s * (kTile * kBlockK), &shared.full[s], x, bi * kTile);
+                tma_load_tile(&maps.plane[1], shared.operand[1].begin() + s * (kTile * kBlockK), &shared.full[s], x, bi * kTile);
+                tma_load_tile(&maps.plane[2], shared.operand[2].begin() + s * (kTile * kBlockK), &shared.full[s], x, bj * kTile);
+                tma_load_tile(&maps.plane[3], shared.operand[3].begin() + s * (kTile * kBlockK), &shared.full[s], x, bj * kTile);
             }
-            if (buf == 0) {
-                stage_tile(a_ptr, bi, k_tile, k_total, tCsA0);
-                stage_tile(b_ptr, bj, k_tile, k_total, tCsB0);
-            } else {
-                stage_tile(a_ptr, bi, k_tile, k_total, tCsA1);
-                stage_tile(b_ptr, bj, k_tile, k_total, tCsB1);
-            }
-            // generic-proxy writes to shared memory must be visible to the tensor-core proxy
-            cutlass::arch::fence_view_async_shared();
-            __syncthreads();
-            if (elect_one_warp) {
+            // tail: the last commits still arrive on the "empty" barriers; do not leave before them
+            for (int kt = max(0, k_steps - kStages); kt < k_steps && ok; ++kt)
+                ok = bounded_wait(shared, &shared.empty[kt % kStages], uint32_t((kt / kStages) & 1), 0x02000000u | uint32_t(kt));
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -----------------------------------------------------------------------
+        // The whole warp runs this loop: the CuTe MMA atom and umma_arrive elect one lane
+        // themselves with elect.sync over the full warp.
+        bool ok = true;
+        for (int seg = 0; seg < segments && ok; ++seg) {
+            const int acc = seg & 1;
+            if (seg >= 2)
+                ok = __all_sync(0xffffffffu, bounded_wait(shared, &shared.free_[acc], uint32_t((seg / 2 - 1) & 1),
+                                                          0x03000000u | uint32_t(seg)));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            tiled_mma.accumulate_ = UMMA::ScaleOut::Zero;
+            const int kt_end = min(k_steps, (seg + 1) * kSegmentSteps);
+            for (int kt = seg * kSegmentSteps; kt < kt_end; ++kt) {
+                const int s = kt % kStages;
+                ok = __all_sync(0xffffffffu, bounded_wait(shared, &shared.full[s], uint32_t((kt / kStages) & 1),
+                                                          0x04000000u | uint32_t(kt)));
+                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int k_block = 0; k_block < size<2>(tCrA0); ++k_block) {
-                    if (buf == 0) gemm(tiled_mma, tCrA0(_, _, k_block), tCrB0(_, _, k_block), tCtAcc);
-                    else gemm(tiled_mma, tCrA1(_, _, k_block), tCrB1(_, _, k_block), tCtAcc);
-                    tiled_mma.accumulate_ = UMMA::ScaleOut::One;
+                for (int kb = 0; kb < size<2>(dXhi); ++kb) {
+                    if (acc == 0) {
+                        gemm(tiled_mma, dXhi(_, _, kb, s), dWhi(_, _, kb, s), tCtAcc0);
+                        tiled_mma.accumulate_ = UMMA::ScaleOut::One;
+                        gemm(tiled_mma, dXlo(_, _, kb, s), dWhi(_, _, kb, s), tCtAcc0);
+                        gemm(tiled_mma, dXhi(_, _, kb, s), dWlo(_, _, kb, s), tCtAcc0);
+                    } else {
+                        gemm(tiled_mma, dXhi(_, _, kb, s), dWhi(_, _, kb, s), tCtAcc1);
+                        tiled_mma.accumulate_ = UMMA::ScaleOut::One;
+                        gemm(tiled_mma, dXlo(_, _, kb, s), dWhi(_, _, kb, s), tCtAcc1);
+                        gemm(tiled_mma, dXhi(_, _, kb, s), dWlo(_, _, kb, s), tCtAcc1);
+                    }
                 }
-                cutlass::arch::umma_arrive(&shared.mma_barrier[buf]);
+                cutlass::arch::umma_arrive(&shared.empty[s]);   // stage reusable once these MMAs have read it
             }
+            if (ok) cutlass::arch::umma_arrive(&shared.ready[acc]);
         }
-        if (!ok) break;
-        // drain: the last one or two commits of the segment have not been waited for yet
-        {
-            const int n = seg_end - seg_begin;
-            const int last = (seg_end - 1) & 1;
-            bool drained = true;
-            if (n >= 2) {
-                drained = bounded_wait(&shared.mma_barrier[last ^ 1], phase[last ^ 1]);
-                phase[last ^ 1] ^= 1;
-            }
-            if (drained) {
-                drained = bounded_wait(&shared.mma_barrier[last], phase[last]);
-                phase[last] ^= 1;
-            }
-            ok = __syncthreads_and(drained);
+    } else {
+        // ---- epilogue: rows 32q .. 32q+31 of the tile, q = warp % 4 (the warp's tensor-memory lanes)
+        const int q = warp & 3;
+        float total[kTile];
+#pragma unroll
+        for (int i = 0; i < kTile; ++i) total[i] = 0.0f;
+        bool ok = true;
+        for (int seg = 0; seg < segments && ok; ++seg) {
+            const int acc = seg & 1;
+            ok = bounded_wait(shared, &shared.ready[acc], uint32_t((seg / 2) & 1), 0x05000000u | uint32_t(seg));
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kTile);
+#pragma unroll
+            for (int c = 0; c < kTile / 16; ++c) {
+                float v[16];
+                tmem_load16(taddr + c * 16, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) total[c * 16 + i] += v[i];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            arrive(&shared.free_[acc]);
         }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        Tensor tDrAcc = make_tensor<float>(shape(tDgC));
-        copy(tiled_t2r, tDtAcc, tDrAcc);
-        cutlass::arch::fence_view_async_tmem_load();
-        if (accumulate || seg_begin > 0) {
-            CUTE_UNROLL
-            for (int i = 0; i < size(tDrAcc); ++i) tDgC(i) += tDrAcc(i);
-        } else {
-            CUTE_UNROLL
-            for (int i = 0; i < size(tDrAcc); ++i) tDgC(i) = tDrAcc(i);
+        if (ok) {
+            float* row = c_ptr + int64_t(bi * kTile + q * 32 + lane) * ldc + bj * kTile;
+#pragma unroll
+            for (int c = 0; c < kTile / 4; ++c) {
+                float4 out = make_float4(total[4 * c], total[4 * c + 1], total[4 * c + 2], total[4 * c + 3]);
+                float4* dst = reinterpret_cast<float4*>(row) + c;
+                if (accumulate) {
+                    const float4 old = *dst;
+                    out.x += old.x; out.y += old.y; out.z += old.z; out.w += old.w;
+                }
+                *dst = out;
+            }
         }
-        // the next segment's MMAs overwrite the accumulator: order them after these loads
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+
+    __syncthreads();
+    if (shared.failed) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, int(shared.first_failure));
+        // let copies that are still in flight land before the shared memory is given back
+        const long long start = clock64();
+        while (clock64() - start < 4000000) {}
         __syncthreads();
     }
-    if (!ok && threadIdx.x == 0) atomicExch(status, 1);
-    __syncthreads();
-    if (elect_one_warp) {
+    if (warp == 0) {
         tmem_allocator.release_allocation_lock();
-        tmem_allocator.free(shared.tmem_base_ptr, kTile);
+        tmem_allocator.free(tmem_base, 2 * kTile);
     }
 }
 
@@ -266,11 +340,32 @@ syrk_tcgen05_kernel(const Element* __restrict__ a_ptr, const Element* __restrict
 
 using namespace qsrtb_tc;
 
+namespace {
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled_entry()
+{
+    static EncodeTiled fn = nullptr;
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiled>(ptr);
+    return fn;
+}
+
+}  // namespace
+
 extern "C" int qsrtb_hessian_tc_workspace_bytes(int64_t chunk_rows, int d, size_t* bytes)
 {
     if (!bytes || chunk_rows <= 0 || d <= 0) return qsrtb_fail(QSRTB_EINVAL, "bad workspace query");
     const int64_t r_pad = (chunk_rows + kBlockK - 1) / kBlockK * kBlockK;
-    *bytes = size_t(2) * size_t(d) * size_t(3 * r_pad) * sizeof(float) + 256;
+    *bytes = size_t(4) * size_t(d) * size_t(r_pad) * sizeof(float) + 256;
     return QSRTB_OK;
 }
 
@@ -279,42 +374,56 @@ extern "C" int qsrtb_hessian_accumulate_tc(const float* rows, const float* weigh
                                            void* workspace, size_t workspace_bytes, int* status_flag,
                                            void* stream)
 {
-    if (!lower || d <= 0 || (d % kTile) != 0 || ld_h < d || n_rows <= 0 || !rows || ld_rows < d)
+    if (!lower || d <= 0 || (d % kTile) != 0 || ld_h < d || (ld_h % 4) != 0 || n_rows <= 0 || !rows || ld_rows < d)
         return qsrtb_fail(QSRTB_EINVAL, "tensor-core Hessian needs d a multiple of 128 and at least one row");
+    if (reinterpret_cast<uintptr_t>(lower) & 15) return qsrtb_fail(QSRTB_EINVAL, "accumulator must be 16-byte aligned");
     if (!status_flag) return qsrtb_fail(QSRTB_EINVAL, "status flag pointer required");
     const int64_t r_pad64 = (n_rows + kBlockK - 1) / kBlockK * kBlockK;
-    if (3 * r_pad64 > (int64_t(1) << 30)) return qsrtb_fail(QSRTB_EINVAL, "row chunk too large");
+    if (r_pad64 > (int64_t(1) << 28)) return qsrtb_fail(QSRTB_EINVAL, "row chunk too large");
     const int r_pad = int(r_pad64);
     size_t need = 0;
     qsrtb_hessian_tc_workspace_bytes(n_rows, d, &need);
     if (!workspace || workspace_bytes < need) return qsrtb_fail(QSRTB_ESCRATCH, "Hessian workspace too small");
+    EncodeTiled encode = encode_tiled_entry();
+    if (!encode) return qsrtb_fail(QSRTB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // 256-byte aligned halves of the workspace
-    uintptr_t base = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255);
-    float* a_split = reinterpret_cast<float*>(base);
-    float* b_split = a_split + size_t(d) * size_t(3 * r_pad);
+    float* planes = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
 
     dim3 grid_t(unsigned(r_pad / 32), unsigned((d + 31) / 32));
-    split_transpose_kernel<<<grid_t, 256, 0, s>>>(rows, weights, n_rows, d, ld_rows, r_pad, a_split, b_split);
+    split_transpose_kernel<<<grid_t, 256, 0, s>>>(rows, weights, n_rows, d, ld_rows, r_pad, planes);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "split_transpose launch");
 
+    // one tensor map per plane: [d rows, r_pad columns] float32, boxes of 128 rows x 32 columns,
+    // 128-byte swizzle (the layout the K-major UMMA descriptors expect)
+    Maps maps;
+    const cuuint64_t dims[2] = {cuuint64_t(r_pad), cuuint64_t(d)};
+    const cuuint64_t strides[1] = {cuuint64_t(r_pad) * sizeof(float)};
+    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kTile)};
+    const cuuint32_t elem[2] = {1, 1};
+    for (int p = 0; p < 4; ++p) {
+        const CUresult rc = encode(&maps.plane[p], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                                   planes + size_t(p) * size_t(d) * size_t(r_pad), dims, strides, box, elem,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc != CUDA_SUCCESS) return qsrtb_fail(QSRTB_ECUDA, "cuTensorMapEncodeTiled failed");
+    }
+
     TiledMMA tiled_mma = make_tiled_mma(
         SM100_MMA_TF32_SS<Element, Element, float, kTile, kTile, UMMA::Major::K, UMMA::Major::K>{});
-    auto mma_tiler = make_shape(Int<kTile>{}, Int<kTile>{}, Int<kBlockK>{});
-    auto mma_shape_A = partition_shape_A(tiled_mma, make_shape(size<0>(mma_tiler), size<2>(mma_tiler)));
-    auto mma_shape_B = partition_shape_B(tiled_mma, make_shape(size<1>(mma_tiler), size<2>(mma_tiler)));
-    auto sA_layout = UMMA::tile_to_mma_shape(UMMA::Layout_K_SW128_Atom<Element>{}, mma_shape_A);
-    auto sB_layout = UMMA::tile_to_mma_shape(UMMA::Layout_K_SW128_Atom<Element>{}, mma_shape_B);
-    using Storage = SharedStorage<decltype(sA_layout), decltype(sB_layout)>;
-    const int smem_bytes = int(sizeof(Storage)) + 128;
-    auto kernel = syrk_tcgen05_kernel<decltype(tiled_mma), decltype(sA_layout), decltype(sB_layout)>;
+    auto mma_shape = partition_shape_A(tiled_mma, make_shape(Int<kTile>{}, Int<kBlockK>{}));
+    auto smem_layout = UMMA::tile_to_mma_shape(UMMA::Layout_K_SW128_Atom<Element>{},
+                                               append(mma_shape, Int<kStages>{}));
+    static_assert(cute::cosize_v<decltype(smem_layout)> == kStages * kTile * kBlockK,
+                  "stages must be 16 KiB apart");
+    using Storage = SharedStorage<decltype(smem_layout)>;
+    const int smem_bytes = int(sizeof(Storage)) + 1024;
+    auto kernel = syrk_tcgen05_kernel<decltype(tiled_mma), decltype(smem_layout)>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaFuncSetAttribute(syrk_tcgen05)");
     const int nb = d / kTile;
-    kernel<<<nb * (nb + 1) / 2, kThreads, smem_bytes, s>>>(
-        reinterpret_cast<const Element*>(a_split), reinterpret_cast<const Element*>(b_split), d, 3 * r_pad,
-        lower, ld_h, accumulate, status_flag, tiled_mma, sA_layout, sB_layout);
+    kernel<<<nb * (nb + 1) / 2, kThreads, smem_bytes, s>>>(maps, d, r_pad / kBlockK, lower, ld_h, accumulate,
+                                                           status_flag, tiled_mma, smem_layout);
     err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "syrk_tcgen05 launch");
     return QSRTB_OK;

@@ -2,9 +2,11 @@
 
 Mirrors ``qsrt/candidate_hessian.py`` (``weighted_covariance``, ``shrink_covariance``,
 ``weighted_effective_sample_size``, ``adaptive_identity_shrinkage``) and the accumulator of
-``qsrt/capture.py:714-731``.  The contraction runs in ``qsrtb_hessian_accumulate`` (weighted
-lower-triangular SYRK, float32 accumulation); the scalar shrinkage statistics stay on the host
-in float64 exactly as in the reference.
+``qsrt/capture.py:714-731``.  The contraction runs on the tensor cores
+(``qsrtb_hessian_accumulate_tc``: TMA-fed tcgen05 3xTF32 with float32 partial sums, within 1e-5
+of FP64) when the feature count is a multiple of 128, otherwise in ``qsrtb_hessian_accumulate``
+(weighted lower-triangular SYRK on the float32 FMA units); the scalar shrinkage statistics stay
+on the host in float64 exactly as in the reference.
 """
 
 from __future__ import annotations
@@ -17,9 +19,23 @@ from . import _lib
 from .tiles import _stream_ptr
 
 
-# Rows handed to one tensor-core launch (its split operands take 24 bytes per row and feature).
+# Rows handed to one tensor-core launch (its split operands take 16 bytes per row and feature).
 TENSOR_CORE_CHUNK_ROWS = 2048
+# Default for ``weighted_covariance(tensor_cores=None)``.
+USE_TENSOR_CORES = True
 _tc_workspace: dict[str, torch.Tensor] = {}
+_tc_built: list[bool] = []
+
+
+def tensor_cores_available() -> bool:
+    """True when the library was built with the tcgen05 Hessian kernel (CuTe headers present)."""
+
+    import ctypes
+
+    if not _tc_built:
+        wanted = ctypes.c_size_t(0)
+        _tc_built.append(_lib.lib().qsrtb_hessian_tc_workspace_bytes(32, 128, ctypes.byref(wanted)) == 0)
+    return _tc_built[0]
 
 
 def accumulate_hessian_tensor_cores(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *,
@@ -63,8 +79,15 @@ def accumulate_hessian_tensor_cores(lower: torch.Tensor, rows: torch.Tensor, wei
                 "qsrtb_hessian_accumulate_tc",
             )
             first = False
-    if int(status.item()) != 0:
-        raise RuntimeError("tensor-core Hessian kernel gave up waiting for its MMAs (status flag set)")
+    code = int(status.item())
+    if code != 0:
+        roles = {1: "producer waiting for a free stage", 2: "producer waiting for the last commits",
+                 3: "MMA issuer waiting for a drained accumulator", 4: "MMA issuer waiting for a loaded stage",
+                 5: "epilogue waiting for a finished segment"}
+        raise RuntimeError(
+            f"tensor-core Hessian kernel gave up: {roles.get(code >> 24, 'unknown wait')} "
+            f"(sequence {code & 0xFFFFFF}, status 0x{code:08x})"
+        )
 
 
 def accumulate_hessian(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *, accumulate: bool = True) -> None:
@@ -106,11 +129,12 @@ def finish_hessian(lower: torch.Tensor, weight_sum: float) -> torch.Tensor:
 
 def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: torch.device,
                         chunk_rows: int = 65536, return_cpu: bool = True,
-                        tensor_cores: bool = False) -> tuple[torch.Tensor, float]:
+                        tensor_cores: bool | None = None) -> tuple[torch.Tensor, float]:
     """Return ``sum(w * x xT) / sum(w)`` as symmetric FP32 (qsrt/candidate_hessian.py:70-112).
 
     ``chunk_rows`` only bounds the staging copy of host-resident rows; the kernel streams any
-    number of rows in one launch.
+    number of rows in one launch.  ``tensor_cores``: ``None`` follows ``USE_TENSOR_CORES``,
+    ``False`` forces the float32 FMA kernel, ``True`` insists on the tensor-core kernel.
     """
 
     if rows.ndim != 2 or weights.ndim != 1 or rows.shape[0] != weights.shape[0]:
@@ -132,7 +156,10 @@ def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: to
         raise ValueError("covariance weights must have a positive finite sum")
     accumulator = torch.empty((dimension, dimension), dtype=torch.float32, device=device)
     first = True
-    use_tc = bool(tensor_cores) and dimension % 128 == 0
+    if tensor_cores is None:
+        use_tc = USE_TENSOR_CORES and dimension % 128 == 0 and tensor_cores_available()
+    else:
+        use_tc = bool(tensor_cores) and dimension % 128 == 0
     for begin in range(0, int(rows.shape[0]), chunk_rows):
         step = accumulate_hessian_tensor_cores if use_tc else accumulate_hessian
         step(accumulator, rows[begin:begin + chunk_rows], weights[begin:begin + chunk_rows], accumulate=not first)
