@@ -19,8 +19,14 @@ from pathlib import Path
 REF_NAME = "qsrt_ref_sqg_ext"
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> Path | None:
-    root = Path(reference_root)
+def default_reference_root() -> str:
+    """The reference checkout: ``$QSRT_REFERENCE_ROOT`` or the ``reference`` folder beside the repository."""
+
+    return os.environ.get("QSRT_REFERENCE_ROOT", str(Path(__file__).resolve().parents[2] / "reference"))
+
+
+def build(reference_root: str | None = None, verbose: bool = False) -> Path | None:
+    root = Path(reference_root or default_reference_root())
     csrc = root / "qsrt" / "csrc"
     out = Path(__file__).resolve().parent / "_ref"
     if not (csrc / "sqg_quantize.cu").exists():

@@ -1,7 +1,7 @@
 """Generate tests/golden/viterbi_golden.npz ON A GPU BOX from the unmodified reference kernel.
 
 Run (from the repository root, after `python oracle/build_ref.py` produced oracle/_ref):
-    python tests/golden/make_viterbi_golden.py gpurun_out/viterbi_golden.npz
+    python tests/golden/make_viterbi_golden.py [output.npz]
 The file holds, for K in {2,3,4} x tailbite context in {1,32,128}, the 16-bit states the
 reference CUDA extension emits for 8 seeded tiles of each input family plus the structural
 rows; inputs are regenerated from the seeds by tests/helpers.py, so only states are stored.
@@ -36,4 +36,4 @@ def main(out_path: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/viterbi_golden.npz")
+    main(sys.argv[1] if len(sys.argv) > 1 else str(ROOT / "tests" / "golden" / "viterbi_golden.npz"))
