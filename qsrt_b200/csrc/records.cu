@@ -10,9 +10,9 @@
 //             which lets three matrices and their scales share one bundle per slot
 //             (qsrt/qsrt_storage.py:194-231,347-362,441-462).
 //
-// The kernels walk the tiles in DESTINATION order (one warp per tile), so every warp writes one
-// contiguous run of 32*K bytes and consecutive warps write consecutive runs; the 512-byte state
-// reads are contiguous per tile wherever the tile lies.  Nothing is materialised in between:
+// One warp per tile: it reads the tile's 512 bytes of states in one piece and writes one
+// contiguous run of 32*K bytes; a block row covers one tile row (column) of the rate axis, so the
+// record, its width and its offset are derived once per block and no index needs a division.  Nothing is materialised in between:
 // states -> final image is one read of the states and one write of the image.
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -43,35 +43,26 @@ struct Placement {
     int bits;
 };
 
-// q-th tile in destination order
-__device__ __forceinline__ Placement place(const RecordLayout& g, int q)
+// Tile `o` (position along the orthogonal axis) of tile row/column `along` of the rate axis.
+// The grid's y index is `along`, so a block derives record and stripe once and its warps step
+// through `o` without any division.
+__device__ __forceinline__ Placement place(const RecordLayout& g, int along, int o)
 {
     Placement p;
-    int record, stripe, o;
+    const int record = along / g.stripes;
+    const int stripe = along - record * g.stripes;
+    p.bits = g.bits[record];
     if (g.layout == 0) {
-        const int per_record = g.stripes * g.orth;
-        record = q / per_record;
-        const int idx = q - record * per_record;
-        if (g.rate_axis == 0) { stripe = idx / g.orth; o = idx - stripe * g.orth; }
-        else                  { o = idx / g.stripes;   stripe = idx - o * g.stripes; }
-        p.bits = g.bits[record];
+        const int idx = g.rate_axis == 0 ? stripe * g.orth + o : o * g.stripes + stripe;
         p.dst32 = g.record_off32[record] + int64_t(idx) * 8 * p.bits;
     } else {
-        const int per_atom = 2 * g.orth;
-        const int atom = q / per_atom;
-        const int rem = q - atom * per_atom;
-        const int side = rem / g.orth;
-        o = rem - side * g.orth;
-        const int pair = atom / g.stripes;
-        stripe = atom - pair * g.stripes;
-        record = 2 * pair + side;
-        p.bits = g.bits[record];
+        const int pair = record >> 1, side = record & 1;
         const int n_atoms = (g.n_records / 2) * g.stripes;
-        const int slot = (atom + g.rotation) % n_atoms;
+        int slot = pair * g.stripes + stripe + g.rotation;
+        if (slot >= n_atoms) slot -= n_atoms;
         p.dst32 = int64_t(slot) * g.atom_pitch32 + (side ? int64_t(g.orth) * 8 * g.bits[2 * pair] : 0) +
                   int64_t(o) * 8 * p.bits;
     }
-    const int along = record * g.stripes + stripe;
     p.src_tile = g.rate_axis == 0 ? int64_t(along) * g.tiles_n + o : int64_t(o) * g.tiles_n + along;
     return p;
 }
@@ -103,9 +94,8 @@ pack_records_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, Record
                     uint32_t* __restrict__ dst, int* __restrict__ open_paths)
 {
     const int lane = threadIdx.x & 31;
-    for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
-         q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement p = place(g, int(q));
+    for (int o = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); o < g.orth; o += gridDim.x * kWarpsPerBlock) {
+        const Placement p = place(g, blockIdx.y, o);
         const int chunk_bits = 8 * p.bits;
         const uint4 v = reinterpret_cast<const uint4*>(states + p.src_tile * 256)[lane];
         const uint32_t chunk = lane_chunk(v, p.bits);
@@ -135,9 +125,8 @@ unpack_records_kernel(const uint32_t* __restrict__ src, int64_t n_tiles, RecordL
                       uint16_t* __restrict__ out_states, uint16_t* __restrict__ out_edges)
 {
     const int lane = threadIdx.x & 31;
-    for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
-         q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement p = place(g, int(q));
+    for (int o = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); o < g.orth; o += gridDim.x * kWarpsPerBlock) {
+        const Placement p = place(g, blockIdx.y, o);
         const int chunk_bits = 8 * p.bits;
         const uint32_t* words = src + p.dst32;
         const int bit0 = lane * chunk_bits;
@@ -170,15 +159,10 @@ records_atoms_kernel(uint32_t* __restrict__ records, int64_t n_tiles, RecordLayo
                      RecordLayout g_atoms, uint32_t* __restrict__ atoms, int to_records)
 {
     const int lane = threadIdx.x & 31;
-    for (int64_t q = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); q < n_tiles;
-         q += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const Placement pa = place(g_atoms, int(q));
-        // the same source tile's position in record order
-        const int tk = int(pa.src_tile / g_atoms.tiles_n), tn = int(pa.src_tile - int64_t(tk) * g_atoms.tiles_n);
-        const int along = g_atoms.rate_axis == 0 ? tk : tn, o = g_atoms.rate_axis == 0 ? tn : tk;
-        const int record = along / g_atoms.stripes, stripe = along - record * g_atoms.stripes;
-        const int idx = g_atoms.rate_axis == 0 ? stripe * g_atoms.orth + o : o * g_atoms.stripes + stripe;
-        const int64_t rec32 = g_records.record_off32[record] + int64_t(idx) * 8 * pa.bits;
+    for (int o = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); o < g_atoms.orth;
+         o += gridDim.x * kWarpsPerBlock) {
+        const Placement pa = place(g_atoms, blockIdx.y, o);
+        const int64_t rec32 = place(g_records, blockIdx.y, o).dst32;
         if (lane < 8 * pa.bits) {
             if (to_records) records[rec32 + lane] = atoms[pa.dst32 + lane];
             else atoms[pa.dst32 + lane] = records[rec32 + lane];
@@ -186,14 +170,11 @@ records_atoms_kernel(uint32_t* __restrict__ records, int64_t n_tiles, RecordLayo
     }
 }
 
-int grid_for_tiles(int64_t n_tiles)
+// grid.y = tile rows (columns) along the rate axis, grid.x covers the orthogonal tiles.
+dim3 grid_for(const RecordLayout& g)
 {
-    int device = 0, sms = 148;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const int64_t wanted = (n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    const int64_t cap = int64_t(sms) * 8;
-    return int(wanted < cap ? (wanted > 0 ? wanted : 1) : cap);
+    const int along = g.n_records * g.stripes;
+    return dim3(unsigned((g.orth + kWarpsPerBlock - 1) / kWarpsPerBlock), unsigned(along));
 }
 
 // Validates the geometry and fills the layout; returns the bytes the destination must hold.
@@ -209,6 +190,7 @@ int make_layout(int tiles_k, int tiles_n, int rate_axis, int n_records, int stri
     const int along = rate_axis == 0 ? tiles_k : tiles_n;
     if (int64_t(n_records) * stripes != along)
         return qsrtb_fail(QSRTB_EINVAL, "records do not cover the rate axis");
+    if (along > 65535) return qsrtb_fail(QSRTB_EINVAL, "rate axis longer than 65535 tiles");
     g->tiles_k = tiles_k; g->tiles_n = tiles_n; g->rate_axis = rate_axis;
     g->n_records = n_records; g->stripes = stripes;
     g->orth = rate_axis == 0 ? tiles_n : tiles_k;
@@ -259,7 +241,7 @@ extern "C" int qsrtb_pack_records(const int16_t* states, int tiles_k, int tiles_
         return qsrtb_fail(QSRTB_EINVAL, "states need 16-byte and the destination 4-byte alignment");
     if (dst_bytes < extent) return qsrtb_fail(QSRTB_EINVAL, "destination too small for the payload");
     const int64_t n_tiles = int64_t(tiles_k) * tiles_n;
-    pack_records_kernel<<<grid_for_tiles(n_tiles), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
+    pack_records_kernel<<<grid_for(g), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(states), n_tiles, g, reinterpret_cast<uint32_t*>(dst), open_paths);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "pack_records launch");
@@ -282,7 +264,7 @@ extern "C" int qsrtb_unpack_records(const int16_t* src, int64_t src_bytes, int t
         return qsrtb_fail(QSRTB_EINVAL, "outputs need 16-byte and the payload 4-byte alignment");
     if (src_bytes < extent) return qsrtb_fail(QSRTB_EINVAL, "payload shorter than its description");
     const int64_t n_tiles = int64_t(tiles_k) * tiles_n;
-    unpack_records_kernel<<<grid_for_tiles(n_tiles), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
+    unpack_records_kernel<<<grid_for(g), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint32_t*>(src), n_tiles, g, reinterpret_cast<uint16_t*>(out_states),
         reinterpret_cast<uint16_t*>(out_edges));
     const cudaError_t err = cudaGetLastError();
@@ -309,7 +291,7 @@ extern "C" int qsrtb_records_atoms(int16_t* records, int64_t records_bytes, int 
     if (records_bytes < extent_records || atoms_bytes < extent_atoms)
         return qsrtb_fail(QSRTB_EINVAL, "buffer shorter than its description");
     const int64_t n_tiles = int64_t(tiles_k) * tiles_n;
-    records_atoms_kernel<<<grid_for_tiles(n_tiles), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
+    records_atoms_kernel<<<grid_for(g_atoms), 32 * kWarpsPerBlock, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<uint32_t*>(records), n_tiles, g_records, g_atoms, reinterpret_cast<uint32_t*>(atoms),
         to_records);
     const cudaError_t err = cudaGetLastError();

@@ -94,36 +94,58 @@ hadamard_rows_kernel(float* __restrict__ x, int batch, int rows, int cols, int l
     }
 }
 
-// block = 128 threads = 128 columns; blockIdx.y = 128-row strip; blockIdx.z = matrix.
+// Column transform (axis 0).  block = 256 threads = 128 columns; blockIdx.y = 128-row strip;
+// blockIdx.z = matrix.  A warp takes 16 columns: lanes 0..15 hold rows 0..63 of their column in
+// registers, lanes 16..31 rows 64..127 of the same columns, so a thread carries 64 values (no
+// local-memory spills) and every load or store instruction moves two full 64-byte row segments.
+// Butterflies of width 1..32 stay inside the thread, width 64 is one shuffle per value with the
+// same operands and rounding as a single 128-value strip would use.
 // MODE: 0 no scaling, 1 scale inputs, 2 scale results; the scaling flavour is compiled in so
-// the unrolled 128-value strip carries no per-element branches.
+// the unrolled strip carries no per-element branches.
 template <int MODE, bool PER_COL, bool DIVIDE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 2)
 hadamard_cols_kernel(float* __restrict__ x, int rows, int cols, int ld, int64_t x_stride,
                      const float* __restrict__ scale, int64_t scale_stride)
 {
-    const int c = blockIdx.x * 128 + threadIdx.x;
-    if (c >= cols) return;
-    const int r0 = blockIdx.y * 128;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4;
+    const int c_want = blockIdx.x * 128 + warp * 16 + (lane & 15);
+    const bool active = c_want < cols;
+    const int c = active ? c_want : cols - 1;   // inactive lanes shadow a valid column for the shuffles
+    const int r0 = blockIdx.y * 128 + half * 64;
     float* base = x + blockIdx.z * x_stride + int64_t(r0) * ld + c;
-    const float* vec = MODE != 0 ? scale + blockIdx.z * scale_stride + (PER_COL ? c : r0) : nullptr;
+    // per-row scales of the strip go through shared memory (one value serves the whole row)
+    __shared__ float row_scale[128];
     float col_s = 1.0f;
-    if constexpr (MODE != 0 && PER_COL) col_s = vec[0];
+    if constexpr (MODE != 0) {
+        const float* vec = scale + blockIdx.z * scale_stride;
+        if constexpr (PER_COL) {
+            col_s = vec[c];
+        } else {
+            if (threadIdx.x < 128) row_scale[threadIdx.x] = vec[blockIdx.y * 128 + threadIdx.x];
+            __syncthreads();
+        }
+    }
     auto scaled = [&](float value, int r) {
-        const float s = PER_COL ? col_s : vec[r];
+        const float s = PER_COL ? col_s : row_scale[half * 64 + r];
         return DIVIDE ? __fdiv_rn(value, s) : value * s;
     };
-    float v[128];
+    float v[64];
 #pragma unroll
-    for (int r = 0; r < 128; ++r) v[r] = base[int64_t(r) * ld];
+    for (int r = 0; r < 64; ++r) v[r] = base[int64_t(r) * ld];
     if constexpr (MODE == 1) {
 #pragma unroll
-        for (int r = 0; r < 128; ++r) v[r] = scaled(v[r], r);
+        for (int r = 0; r < 64; ++r) {
+            v[r] = scaled(v[r], r);
+            // keep the scalings in order: interleaving 64 of them (IEEE divisions above all) with
+            // their row addresses costs more registers than the strip leaves free
+            asm volatile("" : "+f"(v[r]));
+        }
     }
 #pragma unroll
-    for (int bit = 1; bit < 128; bit <<= 1) {
+    for (int bit = 1; bit < 64; bit <<= 1) {
 #pragma unroll
-        for (int r = 0; r < 128; ++r) {
+        for (int r = 0; r < 64; ++r) {
             if ((r & bit) == 0) {
                 const float a = v[r], b = v[r | bit];
                 v[r] = a + b;
@@ -132,13 +154,30 @@ hadamard_cols_kernel(float* __restrict__ x, int rows, int cols, int ld, int64_t 
         }
     }
 #pragma unroll
-    for (int r = 0; r < 128; ++r) v[r] *= kInvSqrt128;
-    if constexpr (MODE == 2) {
-#pragma unroll
-        for (int r = 0; r < 128; ++r) v[r] = scaled(v[r], r);
+    for (int r = 0; r < 64; ++r) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[r], 16);
+        v[r] = half ? other - v[r] : v[r] + other;
     }
 #pragma unroll
-    for (int r = 0; r < 128; ++r) base[int64_t(r) * ld] = v[r];
+    for (int r = 0; r < 64; ++r) {
+        v[r] *= kInvSqrt128;
+        asm volatile("" : "+f"(v[r]));
+    }
+    if constexpr (MODE == 2) {
+#pragma unroll
+        for (int r = 0; r < 64; ++r) {
+            v[r] = scaled(v[r], r);
+            asm volatile("" : "+f"(v[r]));
+        }
+    }
+    if (active) {
+        // a pointer the compiler cannot equate with the load addresses: otherwise it keeps all 64
+        // row addresses alive across the butterflies for the stores and spills
+        float* out = base;
+        asm volatile("" : "+l"(out));
+#pragma unroll
+        for (int r = 0; r < 64; ++r) out[int64_t(r) * ld] = v[r];
+    }
 }
 
 template <int MODE>
@@ -146,11 +185,11 @@ void launch_hadamard_cols(dim3 grid, cudaStream_t s, float* x, int rows, int col
                           const ScaleSpec& sc)
 {
     if (sc.per_col) {
-        if (sc.divide) hadamard_cols_kernel<MODE, true, true><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
-        else hadamard_cols_kernel<MODE, true, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        if (sc.divide) hadamard_cols_kernel<MODE, true, true><<<grid, 256, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        else hadamard_cols_kernel<MODE, true, false><<<grid, 256, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
     } else {
-        if (sc.divide) hadamard_cols_kernel<MODE, false, true><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
-        else hadamard_cols_kernel<MODE, false, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        if (sc.divide) hadamard_cols_kernel<MODE, false, true><<<grid, 256, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
+        else hadamard_cols_kernel<MODE, false, false><<<grid, 256, 0, s>>>(x, rows, cols, ld, x_stride, sc.vec, sc.stride);
     }
 }
 
@@ -187,8 +226,9 @@ __global__ void col_sumsq_fold_kernel(const float* __restrict__ partial, int col
 // loop (qsrt/exl3_encoder_backend.py:372-393, 2152-2153): every 16-column block is multiplied
 // on the right by the inverse of its diagonal block, diagonal blocks and everything above
 // them become zero (identity blocks whose main diagonal is then cleared).
-// grid.x = block column, grid.y = 64-row chunk; 64 threads, one matrix row each.
-__global__ void __launch_bounds__(64)
+// grid.x = block column, grid.y = 256-row chunk; 256 threads, one matrix row each.  Chunks that
+// lie entirely above the block's first sub-diagonal row have nothing to do and leave at once.
+__global__ void __launch_bounds__(256)
 block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
 {
     __shared__ float dl[16][17];
@@ -196,7 +236,8 @@ block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
     const int blk = blockIdx.x;
     const int d0 = blk * 16;
     const int t = threadIdx.x;
-    for (int i = t; i < 256; i += 64) dl[i >> 4][i & 15] = c[int64_t(d0 + (i >> 4)) * ld + d0 + (i & 15)];
+    if (int(blockIdx.y) * 256 + 255 < d0 + 16) return;
+    dl[t >> 4][t & 15] = c[int64_t(d0 + (t >> 4)) * ld + d0 + (t & 15)];
     __syncthreads();
     if (t < 16) {
         // column t of inv(DL): forward substitution on the lower-triangular diagonal block
@@ -213,7 +254,7 @@ block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
         for (int r = 0; r < 16; ++r) inv[r][t] = col[r];
     }
     __syncthreads();
-    const int r = blockIdx.y * 64 + t;
+    const int r = blockIdx.y * 256 + t;
     if (r >= n) return;
     float* row = c + int64_t(r) * ld + d0;
     float out[16];
@@ -223,7 +264,10 @@ block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
     } else {
         float in[16];
 #pragma unroll
-        for (int k = 0; k < 16; ++k) in[k] = row[k];
+        for (int k = 0; k < 4; ++k) {
+            const float4 q = reinterpret_cast<const float4*>(row)[k];
+            in[4 * k] = q.x; in[4 * k + 1] = q.y; in[4 * k + 2] = q.z; in[4 * k + 3] = q.w;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             float s = 0.0f;
@@ -238,16 +282,19 @@ block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
     // kernel race-free the diagonal rows are written by a second launch (zero_diag below).
     if (r >= d0 + 16) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) row[j] = out[j];
+        for (int j = 0; j < 4; ++j)
+            reinterpret_cast<float4*>(row)[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
     }
 }
 
 // Zero the diagonal blocks and everything above them (row r, columns >= 16*floor(r/16)).
-__global__ void block_ldl_zero_upper_kernel(float* __restrict__ c, int n, int ld)
+// One block per row, 16-byte stores from the row's diagonal block to its end.
+__global__ void __launch_bounds__(256)
+block_ldl_zero_upper_kernel(float* __restrict__ c, int n, int ld)
 {
-    const int r = blockIdx.y;
-    const int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col < n && col >= (r & ~15)) c[int64_t(r) * ld + col] = 0.0f;
+    const int r = blockIdx.x;
+    float4* row = reinterpret_cast<float4*>(c + int64_t(r) * ld);
+    for (int q = (r & ~15) / 4 + threadIdx.x; q < n / 4; q += blockDim.x) row[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 }
 
 }  // namespace
@@ -274,7 +321,7 @@ extern "C" int qsrtb_hadamard128(float* x, int batch, int rows, int cols, int ld
                                                              row_sumsq, sumsq_stride);
     } else {
         dim3 grid((cols + 127) / 128, rows / 128, batch);
-        if (!sc.vec) hadamard_cols_kernel<0, false, false><<<grid, 128, 0, s>>>(x, rows, cols, ld, x_stride, nullptr, 0);
+        if (!sc.vec) hadamard_cols_kernel<0, false, false><<<grid, 256, 0, s>>>(x, rows, cols, ld, x_stride, nullptr, 0);
         else if (sc.after) launch_hadamard_cols<2>(grid, s, x, rows, cols, ld, x_stride, sc);
         else launch_hadamard_cols<1>(grid, s, x, rows, cols, ld, x_stride, sc);
     }
@@ -307,12 +354,13 @@ extern "C" int qsrtb_block_ldl_normalize(float* chol, int n, int ld, void* strea
 {
     if (!chol || n < 0 || (n % 16) != 0 || ld < n)
         return qsrtb_fail(QSRTB_EINVAL, "factor must be square with n a multiple of 16");
+    if ((ld % 4) != 0 || (reinterpret_cast<uintptr_t>(chol) & 15))
+        return qsrtb_fail(QSRTB_EINVAL, "factor rows must be 16-byte aligned");
     if (n == 0) return QSRTB_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid(n / 16, (n + 63) / 64);
-    block_ldl_normalize_kernel<<<grid, 64, 0, s>>>(chol, n, ld);
-    dim3 grid2((n + 255) / 256, n);
-    block_ldl_zero_upper_kernel<<<grid2, 256, 0, s>>>(chol, n, ld);
+    dim3 grid(n / 16, (n + 255) / 256);
+    block_ldl_normalize_kernel<<<grid, 256, 0, s>>>(chol, n, ld);
+    block_ldl_zero_upper_kernel<<<n, 256, 0, s>>>(chol, n, ld);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "block_ldl_normalize launch");
     return QSRTB_OK;
