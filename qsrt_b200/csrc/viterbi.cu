@@ -147,10 +147,9 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, c
 
     uint32_t outw[G::P];
     uint32_t dec[G::P];
-#pragma unroll
-    for (int j = 0; j < G::P; ++j) {
+    // Branch metrics of out-edge pair j against all NK predecessors (FP16 FMA pipe).
+    auto metrics = [&](const int j, __half2 (&c)[NK]) {
         const int qq = (2 * j) >> K;  // predecessor group of this pair within the thread
-        __half2 c[NK];
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
             __half2 d;
@@ -187,6 +186,9 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, c
                 c[k] = v;
             }
         }
+    };
+    // Survivor of pair j and its position (ALU pipe).
+    auto select = [&](const int j, __half2 (&c)[NK]) {
         auto r = tournament<0, NK, RECORD, NK>(c);
         if constexpr (MODE == MODE_K2) {
             r.m = __hsub2(r.m, shift2);
@@ -201,6 +203,17 @@ __device__ __forceinline__ void acs_step(const uint32_t (&L)[NL], const int u, c
             for (int b = 0; b < K; ++b) position |= r.bit[b] & (0x00010001u << b);
         }
         dec[j] = position;
+    };
+    // Software pipeline: the metrics of the next pair are issued ahead of this pair's selection,
+    // so that the two math pipes have independent work side by side.
+    {
+        __half2 cbuf[2][NK];
+        metrics(0, cbuf[0]);
+#pragma unroll
+        for (int j = 0; j < G::P; ++j) {
+            if (j + 1 < G::P) metrics(j + 1, cbuf[(j + 1) & 1]);
+            select(j, cbuf[j & 1]);
+        }
     }
 
     // Store the new costs: E consecutive halves.
