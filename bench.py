@@ -38,7 +38,8 @@ def parse_args():
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    p.add_argument("--experts-per-step", type=int, default=2)
+    p.add_argument("--experts-per-step", type=int, default=4,
+                   help="experts encoded together per GPU and step; 4 fills the 148-SM waves of every launch best")
     p.add_argument("--tokens", type=int, default=TOKENS)
     p.add_argument("--hidden", type=int, default=HIDDEN)
     p.add_argument("--inter", type=int, default=INTER)
