@@ -101,7 +101,7 @@ def run_reference(args) -> None:
         "vs_baseline": None,
         "dtype": "f16",
         "data": "synthetic",
-        "config": workload_config(args, 0),
+        "config": workload_config(args, args.experts_per_step),
         "cpu_baseline": {"value": value, "unit": "Mweights/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "Mweights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
