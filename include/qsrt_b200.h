@@ -202,6 +202,13 @@ int qsrtb_ldlq_quantize_members(const float* w, const float* comp, float multipl
 int qsrtb_mxfp4_dequant(const uint8_t* packed, const uint8_t* scale, int out_rows, int in_cols,
                         float* dst, int ld, int transposed, void* stream);
 
+/* No reference counterpart: launches one warp that waits on an mbarrier nothing ever arrives on,
+ * through the same bounded wait the tensor-core Hessian kernel uses.  After about 20 ms the wait
+ * gives up and *status_flag (device int, zeroed by the caller) receives 0x06000000 | lane of the
+ * thread that recorded the expiry; the context stays usable.  For tests of the expiry path.
+ */
+int qsrtb_hessian_tc_wait_probe(int* status_flag, void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).

@@ -51,6 +51,7 @@ _SIGNATURES = {
         _c.c_int,
         [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR, _c.c_size_t, _PTR, _PTR],
     ),
+    "qsrtb_hessian_tc_wait_probe": (_c.c_int, [_PTR, _PTR]),
     "qsrtb_hessian_finish": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _c.c_double, _PTR]),
     "qsrtb_hadamard128": (
         _c.c_int,

@@ -336,6 +336,30 @@ syrk_tcgen05_kernel(const __grid_constant__ Maps maps, int d, int k_steps, float
     }
 }
 
+// A wait that nothing ever satisfies: exercises the bounded-wait path (expiry after kWaitCycles,
+// status word, orderly return) without touching tensor memory or any copy engine.
+struct ProbeStorage {
+    alignas(16) uint64_t barrier;
+    volatile int failed;
+    volatile uint32_t first_failure;
+};
+
+__global__ void __launch_bounds__(32)
+wait_probe_kernel(int* __restrict__ status)
+{
+    __shared__ ProbeStorage shared;
+    if (threadIdx.x == 0) {
+        cute::initialize_barrier(shared.barrier, 1);
+        shared.failed = 0;
+        shared.first_failure = 0;
+        cutlass::arch::fence_barrier_init();
+    }
+    __syncwarp();
+    const bool ok = bounded_wait(shared, &shared.barrier, 0u, 0x06000000u | threadIdx.x);
+    __syncwarp();
+    if (threadIdx.x == 0) atomicCAS(status, 0, ok ? 0 : int(shared.first_failure));
+}
+
 }  // namespace qsrtb_tc
 
 using namespace qsrtb_tc;
@@ -429,7 +453,22 @@ extern "C" int qsrtb_hessian_accumulate_tc(const float* rows, const float* weigh
     return QSRTB_OK;
 }
 
+extern "C" int qsrtb_hessian_tc_wait_probe(int* status_flag, void* stream)
+{
+    if (!status_flag) return qsrtb_fail(QSRTB_EINVAL, "status flag pointer required");
+    wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status_flag);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return qsrtb_fail_cuda(err, "wait_probe launch");
+    return QSRTB_OK;
+}
+
 #else  // QSRTB_NO_CUTLASS
+
+extern "C" int qsrtb_hessian_tc_wait_probe(int*, void*)
+{
+    return qsrtb_fail(QSRTB_EINVAL, "built without the CUTLASS/CuTe headers: tensor-core Hessian unavailable");
+}
+
 
 extern "C" int qsrtb_hessian_tc_workspace_bytes(int64_t, int, size_t*)
 {

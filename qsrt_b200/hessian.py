@@ -38,6 +38,17 @@ def tensor_cores_available() -> bool:
     return _tc_built[0]
 
 
+def tensor_core_wait_probe(device: torch.device) -> int:
+    """Run the tensor-core kernel's bounded wait on a barrier that is never satisfied and return the
+    status word it leaves (``0x06000000 | lane``).  Takes about 20 ms; nothing faults or hangs."""
+
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().qsrtb_hessian_tc_wait_probe(status.data_ptr(), _stream_ptr(device)),
+                   "qsrtb_hessian_tc_wait_probe")
+    return int(status.item())
+
+
 def accumulate_hessian_tensor_cores(lower: torch.Tensor, rows: torch.Tensor, weights: torch.Tensor | None, *,
                                     accumulate: bool = True) -> None:
     """``lower (+)= sum_r w_r x_r x_r^T`` with tcgen05 TF32 MMAs (split operands, float32

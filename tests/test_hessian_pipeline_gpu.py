@@ -239,3 +239,26 @@ def test_full_size_expert_from_mxfp4_sources_k2(cuda_device):
     trellis_bytes = sum(m.trellis.numel() * 2 for m in (payload.w1, payload.w3, payload.w2))
     assert trellis_bytes * 8 == 2 * weights
     assert 0.0 < payload.routed_sse < payload.routed_energy
+
+
+def test_tensor_core_wait_expiry_is_reported_and_harmless(cuda_device):
+    """The tcgen05 Hessian kernel bounds every mbarrier wait.  Here a wait is made to run out on
+    purpose (a barrier nothing arrives on, no tensor memory, no copies in flight): the kernel must
+    return by itself with a status word naming the wait, and the next launch must work."""
+
+    if not hessian.tensor_cores_available():
+        pytest.skip("library built without the CuTe headers")
+    import time
+
+    torch.cuda.synchronize(cuda_device)
+    t0 = time.perf_counter()
+    code = hessian.tensor_core_wait_probe(cuda_device)
+    elapsed = time.perf_counter() - t0
+    assert code >> 24 == 6 and (code & 0xFFFFFF) < 32
+    assert 0.002 < elapsed < 2.0      # about 20 ms of polling, not an endless spin
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn((300, 256), generator=g)
+    w = torch.rand(300, generator=g)
+    cov, _ = hessian.weighted_covariance(x, w, device=cuda_device, tensor_cores=True)
+    ref = (x.double().T * w.double()) @ x.double() / w.double().sum()
+    assert _rel_fro(cov, ref) < 1e-5
