@@ -189,3 +189,60 @@ def test_input_axis_candidates_share_their_backwards_prefix(cuda_device):
         encoder.ldlq_mixed_k_candidates_prefix_reuse(weights, Ls, [[groups[0][0]], [groups[1][0]]])
     with pytest.raises(ValueError, match="mixed_rate_axis='k'"):
         encoder.ldlq_mixed_k_candidates_prefix_reuse(weights, Ls, [[_args(cuda_device, "n", [3] * 16)] * 2] * 2)
+
+
+def test_rate_transfer_candidates_at_native_geometry_pack_into_records_and_atoms(cuda_device):
+    """Reference-native geometry (intermediate 3072, latent 3584): the R0 / R1 / R2 candidates of a
+    down-projection (rate axis K, prefix trie) and of a gate projection (rate axis N, shared K3
+    columns) come out of ``quantize_qsrt_batch`` as closed paths at their records' rates, go into
+    the record container, and from there into atoms and back, bit for bit."""
+
+    from qsrt_b200 import records, storage
+
+    def hessian_data(dim, seed):
+        g = torch.Generator(device=cuda_device).manual_seed(seed)
+        x = torch.randn((4096, dim), device=cuda_device, generator=g)
+        x *= torch.exp(0.5 * torch.randn(dim, device=cuda_device, generator=g))
+        return encoder.make_shared_h(dim, cuda_device, (x.T @ x / 4096).float())
+
+    def candidates(axis, tiles_per_record=8):
+        out = []
+        for mode in ("R0", "R1", "R2"):
+            bits = [b for b in records.record_bits(mode) for _ in range(tiles_per_record)]
+            out.append({
+                "K": 3, "seed": 21, "sv_seed": 22, "sigma_reg": 0.025, "devices": [str(cuda_device)],
+                "device_ratios": None, "apply_out_scales": False, "ldlq_tf32": False, "tailbite_context": 128,
+                "g_scale_override": 0.9, "sqg_e4m3_luts_by_bits": LUTS, "mixed_rate_axis": axis,
+                "mixed_tile_bits": bits,
+            })
+        return out
+
+    g = torch.Generator(device=cuda_device).manual_seed(77)
+    cases = (
+        ("w2", "k", torch.randn((3072, 3584), device=cuda_device, generator=g) * 0.02),   # [K = inter, N = latent]
+        ("w1", "n", torch.randn((3584, 3072), device=cuda_device, generator=g) * 0.02),   # [K = latent, N = inter]
+    )
+    for matrix, axis, weight in cases:
+        assert records.matrix_rate_axis(matrix) == axis
+        results = encoder.quantize_qsrt_batch(
+            [weight.clone()], [hessian_data(weight.shape[0], 5 if axis == "k" else 6)], [candidates(axis)],
+            return_weight_q=True)[0]
+        assert len(results) == 3
+        previous = None
+        for mode, result in zip(("R0", "R1", "R2"), results):
+            states = result["encoded"]
+            assert states.shape == (weight.shape[0] // 16, weight.shape[1] // 16, 256)
+            packed = records.pack_qsrt_trellis(states, mode, rate_axis=axis)   # raises unless every tile closes
+            assert packed.descriptor.payload_bytes == 3072 * 3584 * 3 // 8
+            assert torch.equal(records.unpack_qsrt_trellis_states(packed), states)
+            atoms = storage.pack_matrix_atoms(packed)
+            assert torch.equal(storage.unpack_matrix_atoms(atoms, packed.descriptor).payload, packed.payload)
+            rel = float(((result["weight_q"] - weight) ** 2).mean() / (weight ** 2).mean())
+            assert rel < 0.2 and 0.0 < result["proxy"] < 0.2
+            if previous is not None:
+                # the records both schedules keep at K3 beyond the transferred pairs are shared work
+                if axis == "k":
+                    assert torch.equal(states[4 * 8:], previous[4 * 8:])
+                else:
+                    assert torch.equal(states[:, 4 * 8:], previous[:, 4 * 8:])
+            previous = states
