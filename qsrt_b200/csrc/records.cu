@@ -89,34 +89,47 @@ __device__ __forceinline__ void lane_states(uint32_t chunk, uint32_t prev, int b
     for (int i = 0; i < 8; ++i) st[i] = uint32_t(window >> ((7 - i) * bits)) & 0xffffu;
 }
 
+// Packs one tile held as a lane-distributed uint4 and, when asked, counts it if it is not a closed
+// cyclic walk: every 16-bit state must equal the window of the last ceil(16/K) edge symbols
+// (qsrt/qsrt.py:1074-1078).
+__device__ __forceinline__ void pack_one(const uint4 v, const Placement& p, int lane, uint32_t* __restrict__ dst,
+                                         int* __restrict__ open_paths)
+{
+    const int chunk_bits = 8 * p.bits;
+    const uint32_t chunk = lane_chunk(v, p.bits);
+    if (open_paths) {
+        const uint32_t prev = __shfl_sync(0xffffffffu, chunk, (lane + 31) & 31);
+        uint32_t st[8];
+        lane_states(chunk, prev, p.bits, st);
+        const bool same = v.x == (st[0] | (st[1] << 16)) && v.y == (st[2] | (st[3] << 16)) &&
+                          v.z == (st[4] | (st[5] << 16)) && v.w == (st[6] | (st[7] << 16));
+        const unsigned bad = __ballot_sync(0xffffffffu, !same);
+        if (bad && lane == 0) atomicAdd(open_paths, 1);
+    }
+    const int a = (32 * lane) / chunk_bits;
+    const int off = 32 * lane - a * chunk_bits;
+    const uint32_t ca = __shfl_sync(0xffffffffu, chunk, a & 31);
+    const uint32_t cb = __shfl_sync(0xffffffffu, chunk, (a + 1) & 31);
+    const unsigned long long both = (static_cast<unsigned long long>(ca) << chunk_bits) | cb;
+    const uint32_t word = uint32_t(both >> (2 * chunk_bits - off - 32));
+    if (lane < chunk_bits) dst[p.dst32 + lane] = word;
+}
+
+// Two tiles per warp and iteration: both 512-byte loads are issued before either is consumed.
 __global__ void __launch_bounds__(32 * kWarpsPerBlock)
 pack_records_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, RecordLayout g,
                     uint32_t* __restrict__ dst, int* __restrict__ open_paths)
 {
     const int lane = threadIdx.x & 31;
-    for (int o = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); o < g.orth; o += gridDim.x * kWarpsPerBlock) {
-        const Placement p = place(g, blockIdx.y, o);
-        const int chunk_bits = 8 * p.bits;
-        const uint4 v = reinterpret_cast<const uint4*>(states + p.src_tile * 256)[lane];
-        const uint32_t chunk = lane_chunk(v, p.bits);
-        if (open_paths) {
-            // a stored path must be a closed cyclic walk: every 16-bit state equals the window
-            // of the last ceil(16/K) edge symbols (qsrt/qsrt.py:1074-1078)
-            const uint32_t prev = __shfl_sync(0xffffffffu, chunk, (lane + 31) & 31);
-            uint32_t st[8];
-            lane_states(chunk, prev, p.bits, st);
-            const bool same = v.x == (st[0] | (st[1] << 16)) && v.y == (st[2] | (st[3] << 16)) &&
-                              v.z == (st[4] | (st[5] << 16)) && v.w == (st[6] | (st[7] << 16));
-            const unsigned bad = __ballot_sync(0xffffffffu, !same);
-            if (bad && lane == 0) atomicAdd(open_paths, 1);
-        }
-        const int a = (32 * lane) / chunk_bits;
-        const int off = 32 * lane - a * chunk_bits;
-        const uint32_t ca = __shfl_sync(0xffffffffu, chunk, a & 31);
-        const uint32_t cb = __shfl_sync(0xffffffffu, chunk, (a + 1) & 31);
-        const unsigned long long both = (static_cast<unsigned long long>(ca) << chunk_bits) | cb;
-        const uint32_t word = uint32_t(both >> (2 * chunk_bits - off - 32));
-        if (lane < chunk_bits) dst[p.dst32 + lane] = word;
+    const int stride = gridDim.x * kWarpsPerBlock;
+    for (int o = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); o < g.orth; o += 2 * stride) {
+        const bool pair = o + stride < g.orth;
+        const Placement p0 = place(g, blockIdx.y, o);
+        const Placement p1 = place(g, blockIdx.y, pair ? o + stride : o);
+        const uint4 v0 = reinterpret_cast<const uint4*>(states + p0.src_tile * 256)[lane];
+        const uint4 v1 = reinterpret_cast<const uint4*>(states + p1.src_tile * 256)[lane];
+        pack_one(v0, p0, lane, dst, open_paths);
+        if (pair) pack_one(v1, p1, lane, dst, open_paths);
     }
 }
 
@@ -174,7 +187,8 @@ records_atoms_kernel(uint32_t* __restrict__ records, int64_t n_tiles, RecordLayo
 dim3 grid_for(const RecordLayout& g)
 {
     const int along = g.n_records * g.stripes;
-    return dim3(unsigned((g.orth + kWarpsPerBlock - 1) / kWarpsPerBlock), unsigned(along));
+    // each warp takes two tiles per iteration
+    return dim3(unsigned((g.orth + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock)), unsigned(along));
 }
 
 // Validates the geometry and fills the layout; returns the bytes the destination must hold.
