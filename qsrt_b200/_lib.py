@@ -102,7 +102,7 @@ _KERNELS_PER_CALL = {
     "qsrtb_hessian_tc_workspace_bytes": 0,
     "qsrtb_hessian_accumulate_tc": 2,
     "qsrtb_col_sumsq": 2,
-    "qsrtb_block_ldl_normalize": 2,
+    "qsrtb_block_ldl_normalize": 3,
     "qsrtb_signed_block_hadamard": 1,
 }
 launch_counts: dict[str, int] = {}

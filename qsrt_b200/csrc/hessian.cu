@@ -92,23 +92,38 @@ weighted_syrk_lower_kernel(const float* __restrict__ x, const float* __restrict_
     }
 }
 
-// lower triangle / denom -> full symmetric matrix
-__global__ void finish_symmetric_kernel(float* __restrict__ c, int d, int ldc, float denom)
+// lower triangle / denom -> full symmetric matrix.  One block (32 x 8 threads) per 32 x 32 tile
+// of the lower triangle (tile pairs enumerated in one dimension, so no block is idle); a thread
+// moves four elements of the tile and four of its mirror image.
+__global__ void __launch_bounds__(256)
+finish_symmetric_kernel(float* __restrict__ c, int d, int ldc, float denom)
 {
     __shared__ float tile[32][33];
-    const int bi = blockIdx.y, bj = blockIdx.x;
-    if (bj > bi) return;
-    const int i = bi * 32 + threadIdx.y, j = bj * 32 + threadIdx.x;
-    float v = 0.0f;
-    if (i < d && j < d && j <= i) {
-        v = __fdiv_rn(c[int64_t(i) * ldc + j], denom);
-        c[int64_t(i) * ldc + j] = v;
+    int bi = int((sqrtf(8.0f * float(blockIdx.x) + 1.0f) - 1.0f) * 0.5f);
+    while ((bi + 1) * (bi + 2) / 2 <= int(blockIdx.x)) ++bi;
+    while (bi * (bi + 1) / 2 > int(blockIdx.x)) --bi;
+    const int bj = int(blockIdx.x) - bi * (bi + 1) / 2;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = bi * 32 + ty + 8 * k, j = bj * 32 + tx;
+        v[k] = (i < d && j < d && j <= i) ? c[int64_t(i) * ldc + j] : 0.0f;
     }
-    tile[threadIdx.y][threadIdx.x] = v;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = bi * 32 + ty + 8 * k, j = bj * 32 + tx;
+        v[k] = __fdiv_rn(v[k], denom);
+        if (i < d && j < d && j <= i) c[int64_t(i) * ldc + j] = v[k];
+        tile[ty + 8 * k][tx] = v[k];
+    }
     __syncthreads();
-    // transposed store: element (row = bj*32 + ty, col = bi*32 + tx) strictly above the diagonal
-    const int ti = bj * 32 + threadIdx.y, tj = bi * 32 + threadIdx.x;
-    if (ti < d && tj < d && tj > ti) c[int64_t(ti) * ldc + tj] = tile[threadIdx.x][threadIdx.y];
+    // transposed store: element (row = bj*32 + r, col = bi*32 + tx) strictly above the diagonal
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int ti = bj * 32 + ty + 8 * k, tj = bi * 32 + tx;
+        if (ti < d && tj < d && tj > ti) c[int64_t(ti) * ldc + tj] = tile[tx][ty + 8 * k];
+    }
 }
 
 }  // namespace
@@ -139,7 +154,7 @@ extern "C" int qsrtb_hessian_finish(float* h, int d, int ld_h, double weight_sum
     if (!h || d <= 0 || ld_h < d) return qsrtb_fail(QSRTB_EINVAL, "bad Hessian arguments");
     if (!(weight_sum > 0.0)) return qsrtb_fail(QSRTB_EINVAL, "covariance weights must have a positive finite sum");
     const int nb = (d + 31) / 32;
-    finish_symmetric_kernel<<<dim3(nb, nb), dim3(32, 32), 0, static_cast<cudaStream_t>(stream)>>>(
+    finish_symmetric_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         h, d, ld_h, float(weight_sum));
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "hessian_finish launch");

@@ -225,20 +225,22 @@ __global__ void col_sumsq_fold_kernel(const float* __restrict__ partial, int col
 // Turn a lower Cholesky factor C into the unit block-lower LDL factor used by the feedback
 // loop (qsrt/exl3_encoder_backend.py:372-393, 2152-2153): every 16-column block is multiplied
 // on the right by the inverse of its diagonal block, diagonal blocks and everything above
-// them become zero (identity blocks whose main diagonal is then cleared).
-// grid.x = block column, grid.y = 256-row chunk; 256 threads, one matrix row each.  Chunks that
-// lie entirely above the block's first sub-diagonal row have nothing to do and leave at once.
-__global__ void __launch_bounds__(256)
-block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
+// them become zero (identity blocks whose main diagonal is then cleared).  Three launches:
+//   inverse : one warp per diagonal block inverts it by forward substitution and parks the
+//             result in the tile to its right (above the diagonal: free until the last launch);
+//   apply   : grid.x = block column, grid.y = 256-row chunk below it; a thread multiplies its
+//             row's 16 values by the parked inverse;
+//   zero    : diagonal blocks and everything above them, the parked inverses included.
+// The last block column has no rows below it and needs no inverse.
+__global__ void __launch_bounds__(32)
+block_ldl_inverse_kernel(float* __restrict__ c, int ld)
 {
     __shared__ float dl[16][17];
-    __shared__ float inv[16][17];
-    const int blk = blockIdx.x;
-    const int d0 = blk * 16;
+    const int d0 = blockIdx.x * 16;
     const int t = threadIdx.x;
-    if (int(blockIdx.y) * 256 + 255 < d0 + 16) return;
-    dl[t >> 4][t & 15] = c[int64_t(d0 + (t >> 4)) * ld + d0 + (t & 15)];
-    __syncthreads();
+#pragma unroll
+    for (int i = t; i < 256; i += 32) dl[i >> 4][i & 15] = c[int64_t(d0 + (i >> 4)) * ld + d0 + (i & 15)];
+    __syncwarp();
     if (t < 16) {
         // column t of inv(DL): forward substitution on the lower-triangular diagonal block
         float col[16];
@@ -251,40 +253,38 @@ block_ldl_normalize_kernel(float* __restrict__ c, int n, int ld)
             col[r] = (r < t) ? 0.0f : s / dl[r][r];
         }
 #pragma unroll
-        for (int r = 0; r < 16; ++r) inv[r][t] = col[r];
+        for (int r = 0; r < 16; ++r) c[int64_t(d0 + r) * ld + d0 + 16 + t] = col[r];
     }
+}
+
+__global__ void __launch_bounds__(256)
+block_ldl_apply_kernel(float* __restrict__ c, int n, int ld)
+{
+    __shared__ float inv[16][17];
+    const int d0 = blockIdx.x * 16;
+    const int t = threadIdx.x;
+    if (int(blockIdx.y) * 256 + 255 < d0 + 16) return;
+    inv[t >> 4][t & 15] = c[int64_t(d0 + (t >> 4)) * ld + d0 + 16 + (t & 15)];
     __syncthreads();
     const int r = blockIdx.y * 256 + t;
-    if (r >= n) return;
+    if (r >= n || r < d0 + 16) return;
     float* row = c + int64_t(r) * ld + d0;
-    float out[16];
-    if (r < d0 + 16) {
+    float in[16], out[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) out[j] = 0.0f;
-    } else {
-        float in[16];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float4 q = reinterpret_cast<const float4*>(row)[k];
-            in[4 * k] = q.x; in[4 * k + 1] = q.y; in[4 * k + 2] = q.z; in[4 * k + 3] = q.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float s = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) s += in[k] * inv[k][j];
-            out[j] = s;
-        }
+    for (int k = 0; k < 4; ++k) {
+        const float4 q = reinterpret_cast<const float4*>(row)[k];
+        in[4 * k] = q.x; in[4 * k + 1] = q.y; in[4 * k + 2] = q.z; in[4 * k + 3] = q.w;
     }
-    // The diagonal block is read by every chunk of this block column: chunks that own rows
-    // of the diagonal block must not overwrite it before the others have loaded it.  Those
-    // rows are handled by the chunk(s) with r < d0 + 16, which write zeros; to keep the
-    // kernel race-free the diagonal rows are written by a second launch (zero_diag below).
-    if (r >= d0 + 16) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            reinterpret_cast<float4*>(row)[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+    for (int j = 0; j < 16; ++j) {
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) s += in[k] * inv[k][j];
+        out[j] = s;
     }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        reinterpret_cast<float4*>(row)[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
 }
 
 // Zero the diagonal blocks and everything above them (row r, columns >= 16*floor(r/16)).
@@ -358,8 +358,11 @@ extern "C" int qsrtb_block_ldl_normalize(float* chol, int n, int ld, void* strea
         return qsrtb_fail(QSRTB_EINVAL, "factor rows must be 16-byte aligned");
     if (n == 0) return QSRTB_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid(n / 16, (n + 255) / 256);
-    block_ldl_normalize_kernel<<<grid, 256, 0, s>>>(chol, n, ld);
+    const int columns = n / 16 - 1;   // block columns with rows below them
+    if (columns > 0) {
+        block_ldl_inverse_kernel<<<columns, 32, 0, s>>>(chol, ld);
+        block_ldl_apply_kernel<<<dim3(columns, (n + 255) / 256), 256, 0, s>>>(chol, n, ld);
+    }
     block_ldl_zero_upper_kernel<<<n, 256, 0, s>>>(chol, n, ld);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "block_ldl_normalize launch");
