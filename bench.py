@@ -385,7 +385,7 @@ def run_b200(args) -> None:
             "unit": "G branch metrics/s",
             "frac": achieved / peak if peak > 0 else None,
             # DRAM bytes per launch: one ncu capture of this kernel on 592 tiles measured
-            # 1 104.7 MB read + written = 1.866 MB per tile (the survivor rows); the traffic grows
+            # 1 107.7 MB read + written = 1.871 MB per tile (the survivor rows); the traffic grows
             # in proportion to the tiles, so it is scaled to this run's average launch.
             "traffic": NCU_DRAM_BYTES_PER_TILE * search_tiles / max(search_launches, 1),
             "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 592-tile launch, scaled per tile",
@@ -441,7 +441,7 @@ def cpu_tile_baseline(payload) -> dict:
     }
 
 
-NCU_DRAM_BYTES_PER_TILE = (817.1e6 + 287.6e6) / 592
+NCU_DRAM_BYTES_PER_TILE = (817.4e6 + 290.3e6) / 592
 
 
 def main() -> None:
