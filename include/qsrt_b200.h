@@ -209,6 +209,15 @@ int qsrtb_mxfp4_dequant(const uint8_t* packed, const uint8_t* scale, int out_row
  */
 int qsrtb_hessian_tc_wait_probe(int* status_flag, void* stream);
 
+/* ---- C1/C2: per-tile error surfaces for rate allocation ---------------------------------------
+ * Replaces tile_squared_error and the final tile reduction of dense_h_tile_error_contributions
+ * (qsrt/high_rate_allocation.py:55-73,136-148).  a, b [rows, cols] float32 (row pitches lda, ldb)
+ * -> out [rows/16, cols/16] float64: mode 0 sums (b - a)^2, mode 1 sums a * b over each 16x16
+ * tile; terms are rounded to float32 and added in float64 as in the reference.
+ */
+int qsrtb_tile_reduce(const float* a, const float* b, int rows, int cols, int lda, int ldb, int mode,
+                      double* out, void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).

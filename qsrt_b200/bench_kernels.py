@@ -15,7 +15,7 @@ import json
 
 import torch
 
-from . import codec, coupled, encoder, hessian, mxfp4, records, storage, tables
+from . import allocation, codec, coupled, encoder, hessian, mxfp4, records, storage, tables
 
 
 _flush = None
@@ -109,7 +109,9 @@ def main() -> None:
     mx_packed = torch.randint(0, 256, (mx_rows, mx_cols // 2), device=dev, dtype=torch.uint8, generator=g)
     mx_scale = torch.randint(110, 130, (mx_rows, mx_cols // 32), device=dev, dtype=torch.uint8, generator=g)
     mx_bytes = mx_rows * mx_cols * 4 + mx_packed.numel() + mx_scale.numel()
+    w_other = torch.randn((k, n), device=dev, generator=g)
     cases = {
+        "tile_squared_error": (lambda: allocation.tile_squared_error(w, w_other), 8 * k * n + k * n // 32, "B"),
         "mxfp4_dequant [out, in]": (lambda: mxfp4.dequant(mx_packed, mx_scale), mx_bytes, "B"),
         "mxfp4_dequant -> encoder orientation [in, out]":
             (lambda: mxfp4.dequant_encoder_orientation(mx_packed, mx_scale), mx_bytes, "B"),

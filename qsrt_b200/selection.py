@@ -185,3 +185,208 @@ def equal_byte_exchange(table: torch.Tensor, *, rates: Sequence[int] = (2, 3, 4)
     total_sse = float(sum(sse[e, bits[e] - 2] for e in range(experts)))
     total_bytes = float(sum(size[e, bits[e] - 2] for e in range(experts)))
     return RateAllocation(tuple(bits), total_sse, total_bytes, exchanges, baseline)
+
+
+# ---- phase-1 rate selection with a bootstrap gate (qsrt/qsrt_candidates.py:657-898) -------------
+
+PHASE1_MODE_IDS = (0, 1, 2)
+PHASE1_MIN_FIT_DOCUMENTS = 6
+PHASE1_MIN_CONFIRMATION_DOCUMENTS = 4
+PHASE1_BOOTSTRAP_REPLICATES = 2_000
+PHASE1_SELECTION_SEED = 20_260_801
+
+
+@dataclass(frozen=True)
+class ModeSelection:
+    """A mode proposed on the fit documents and gated on the confirmation documents."""
+
+    proposed_r: int
+    selected_r: int
+    accepted: bool
+    reason: str
+    fit_documents: int
+    confirmation_documents: int
+    confirmation_relative_improvement: float | None
+    confirmation_ci95: tuple[float | None, float | None]
+    bootstrap_replicates_valid: int
+
+
+@dataclass(frozen=True)
+class RatePairSelection:
+    """An ``(r13, r2)`` pair ranked and gated on the confirmation documents."""
+
+    proposed_r13: int
+    proposed_r2: int
+    selected_r13: int
+    selected_r2: int
+    accepted: bool
+    reason: str
+    fit_documents: int
+    confirmation_documents: int
+    confirmation_relative_improvement: float | None
+    confirmation_ci95: tuple[float | None, float | None]
+    bootstrap_replicates_valid: int
+
+    @property
+    def proposed(self) -> tuple[int, int]:
+        return self.proposed_r13, self.proposed_r2
+
+    @property
+    def selected(self) -> tuple[int, int]:
+        return self.selected_r13, self.selected_r2
+
+
+def bootstrap_improvement(baseline: torch.Tensor, candidate: torch.Tensor, support: torch.Tensor, *,
+                          replicates: int, seed: int):
+    """Relative SSE improvement ``1 - sum(candidate) / sum(baseline)`` over the supported documents
+    and its 95 % bootstrap interval (qsrt/qsrt_candidates.py:657-696).
+
+    Documents are resampled with replacement by ``numpy.random.default_rng(seed)`` in batches of
+    at most 512 replicates, exactly as in the reference, so the interval is reproducible bit for
+    bit.  Returns ``(observed, (low, high), valid_replicates)``; ``None`` where undefined.
+    """
+
+    import numpy as np
+
+    if replicates < 100:
+        raise ValueError("bootstrap replicates must be at least 100")
+    if baseline.shape != candidate.shape or baseline.ndim != 1:
+        raise ValueError("bootstrap SSE vectors must be equal one-dimensional shapes")
+    if support.dtype != torch.bool or support.shape != baseline.shape:
+        raise ValueError("bootstrap support mask has the wrong shape")
+    base = baseline[support].double().cpu().numpy()
+    trial = candidate[support].double().cpu().numpy()
+    if base.size == 0 or not np.isfinite(base).all() or not np.isfinite(trial).all():
+        return None, (None, None), 0
+    total = float(base.sum())
+    if total <= 0:
+        return None, (None, None), 0
+    observed = 1.0 - float(trial.sum()) / total
+    rng = np.random.default_rng(int(seed))
+    kept = []
+    left = int(replicates)
+    while left:
+        count = min(left, 512)
+        draw = rng.integers(0, base.size, size=(count, base.size))
+        drawn_base, drawn_trial = base[draw].sum(axis=1), trial[draw].sum(axis=1)
+        usable = drawn_base > 0
+        if np.any(usable):
+            kept.append(1.0 - drawn_trial[usable] / drawn_base[usable])
+        left -= count
+    if not kept:
+        return observed, (None, None), 0
+    samples = np.concatenate(kept)
+    low, high = np.quantile(samples, (0.025, 0.975)).tolist()
+    return observed, (float(low), float(high)), int(samples.size)
+
+
+def _gate_reason(interval, minimum_improvement: float) -> tuple[bool, str]:
+    if interval[0] is None:
+        return False, "confirmation bootstrap has no valid baseline samples"
+    if interval[0] <= minimum_improvement:
+        return False, "confirmation lower confidence bound did not clear the margin"
+    return True, "confirmation lower confidence bound cleared the margin"
+
+
+def select_phase1_mode(fit_sse, confirmation_sse, *, fit_counts: torch.Tensor, confirmation_counts: torch.Tensor,
+                       mode_ids: Sequence[int] = PHASE1_MODE_IDS, min_fit_documents: int = PHASE1_MIN_FIT_DOCUMENTS,
+                       min_confirmation_documents: int = PHASE1_MIN_CONFIRMATION_DOCUMENTS,
+                       minimum_improvement: float = 0.0, bootstrap_replicates: int = PHASE1_BOOTSTRAP_REPLICATES,
+                       seed: int = PHASE1_SELECTION_SEED) -> ModeSelection:
+    """Propose the fit-document argmin and accept it only if the lower end of the confirmation
+    documents' bootstrap interval clears the margin (qsrt/qsrt_candidates.py:699-790)."""
+
+    modes = tuple(int(m) for m in mode_ids)
+    if not modes or modes[0] != 0 or len(set(modes)) != len(modes):
+        raise ValueError("mode_ids must be unique and begin with R0")
+    if set(fit_sse) != set(modes) or set(confirmation_sse) != set(modes):
+        raise ValueError("SSE tables must contain every requested mode")
+    fit_support, confirmation_support = fit_counts > 0, confirmation_counts > 0
+    fit_documents, confirmation_documents = int(fit_support.sum()), int(confirmation_support.sum())
+
+    def decision(proposed, selected, accepted, reason, improvement=None, interval=(None, None), valid=0):
+        return ModeSelection(proposed, selected, accepted, reason, fit_documents, confirmation_documents,
+                             improvement, interval, valid)
+
+    if fit_documents < min_fit_documents:
+        return decision(0, 0, False, "insufficient fit-document support")
+    proposed = min(modes, key=lambda m: (float(fit_sse[m][fit_support].double().sum()), m))
+    if proposed == 0:
+        return decision(0, 0, False, "R0 is the fit-document argmin")
+    improvement, interval, valid = bootstrap_improvement(
+        confirmation_sse[0], confirmation_sse[proposed], confirmation_support,
+        replicates=bootstrap_replicates, seed=seed)
+    cleared, reason = _gate_reason(interval, minimum_improvement)
+    if confirmation_documents < min_confirmation_documents:
+        cleared, reason = False, "insufficient confirmation-document support"
+    return decision(proposed, proposed if cleared else 0, cleared, reason, improvement, interval, valid)
+
+
+def select_phase1_rate_pair(fit_sse, confirmation_sse, *, fit_counts: torch.Tensor, confirmation_counts: torch.Tensor,
+                            modes: Sequence[tuple[int, int]], min_fit_documents: int = PHASE1_MIN_FIT_DOCUMENTS,
+                            min_confirmation_documents: int = PHASE1_MIN_CONFIRMATION_DOCUMENTS,
+                            minimum_improvement: float = 0.0, bootstrap_replicates: int = PHASE1_BOOTSTRAP_REPLICATES,
+                            seed: int = PHASE1_SELECTION_SEED) -> RatePairSelection:
+    """Rank the ``(r13, r2)`` grid on the confirmation documents (the fit documents built the
+    encoder's Hessians and only have to exist) and bootstrap-gate the winner against R0/R0
+    (qsrt/qsrt_candidates.py:793-898).  Ties go to fewer transfers, then the smaller r13, r2."""
+
+    candidates = tuple((int(a), int(b)) for a, b in modes)
+    if not candidates or candidates[0] != (0, 0) or len(set(candidates)) != len(candidates):
+        raise ValueError("rate-pair candidates must be unique and begin with R0/R0")
+    if set(fit_sse) != set(candidates) or set(confirmation_sse) != set(candidates):
+        raise ValueError("rate-pair SSE tables must contain every requested candidate")
+    fit_support, confirmation_support = fit_counts > 0, confirmation_counts > 0
+    fit_documents, confirmation_documents = int(fit_support.sum()), int(confirmation_support.sum())
+
+    def decision(proposed, selected, accepted, reason, improvement=None, interval=(None, None), valid=0):
+        return RatePairSelection(proposed[0], proposed[1], selected[0], selected[1], accepted, reason,
+                                 fit_documents, confirmation_documents, improvement, interval, valid)
+
+    if fit_documents < min_fit_documents:
+        return decision((0, 0), (0, 0), False, "insufficient fit-document support")
+    if confirmation_documents < min_confirmation_documents:
+        return decision((0, 0), (0, 0), False, "insufficient confirmation-document support")
+    proposed = min(candidates, key=lambda p: (float(confirmation_sse[p][confirmation_support].double().sum()),
+                                               p[0] + p[1], p[0], p[1]))
+    if proposed == (0, 0):
+        return decision(proposed, proposed, False, "R0/R0 is the confirmation-document argmin")
+    improvement, interval, valid = bootstrap_improvement(
+        confirmation_sse[(0, 0)], confirmation_sse[proposed], confirmation_support,
+        replicates=bootstrap_replicates, seed=seed)
+    cleared, reason = _gate_reason(interval, minimum_improvement)
+    return decision(proposed, proposed if cleared else (0, 0), cleared, reason, improvement, interval, valid)
+
+
+def select_coupled_modes(matrix_sse, families) -> dict:
+    """Minimum total SSE per coupled matrix family, ties to the lower mode
+    (qsrt/qsrt_codec_pilot.py:760-798).  ``matrix_sse[matrix][mode]`` are per-matrix errors and
+    ``families[name]`` the matrices that must share one mode; the families must partition the
+    matrices exactly."""
+
+    if not matrix_sse or not families:
+        raise ValueError("mode selection requires matrices and families")
+    covered: list[str] = []
+    out: dict[str, dict] = {}
+    for family, matrices in families.items():
+        members = tuple(matrices)
+        if not members:
+            raise ValueError(f"rate family {family!r} is empty")
+        covered.extend(members)
+        if members[0] not in matrix_sse:
+            raise KeyError(f"unknown matrix in rate family {family!r}")
+        ladder = set(matrix_sse[members[0]])
+        for matrix in members[1:]:
+            if matrix not in matrix_sse:
+                raise KeyError(f"unknown matrix {matrix!r}")
+            if set(matrix_sse[matrix]) != ladder:
+                raise ValueError("coupled matrices do not share one mode ladder")
+        totals = {int(mode): sum(float(matrix_sse[m][mode]) for m in members) for mode in ladder}
+        if not totals or any(not math.isfinite(v) or v < 0.0 for v in totals.values()):
+            raise ValueError("mode SSE must be finite and nonnegative")
+        best = min(totals, key=lambda mode: (totals[mode], mode))
+        out[str(family)] = {"matrices": list(members), "selected_mode": int(best),
+                            "sse_by_mode": {f"R{mode}": totals[mode] for mode in sorted(totals)}}
+    if len(covered) != len(set(covered)) or set(covered) != set(matrix_sse):
+        raise ValueError("rate families must partition the codec matrices exactly")
+    return out

@@ -132,3 +132,48 @@ def expert_case_inputs():
         local[matrix] = (rng.standard_normal(3072) * 0.1).astype(np.float16)
         shared[matrix] = (rng.standard_normal(3584) * 0.1).astype(np.float16)
     return states, local, shared
+
+
+# ---- phase-1 selection cases (seeded per-document SSE tables) ------------------------------------
+COUPLED_MODE_CASE = (
+    {"w1": {0: 3.0, 1: 2.0, 2: 2.5}, "w3": {0: 3.0, 1: 2.6, 2: 2.0}, "w2": {0: 1.0, 1: 1.0, 2: 4.0}},
+    {"r13": ("w1", "w3"), "r2": ("w2",)},
+)
+
+
+def phase1_case(trial: int) -> dict:
+    """Per-document SSE of the nine ``(r13, r2)`` candidates on a fit and a confirmation fold."""
+
+    g = torch.Generator().manual_seed(6000 + trial)
+    documents = 8 + 2 * trial
+    pairs = tuple((a, b) for a in (0, 1, 2) for b in (0, 1, 2))
+    fit = {p: torch.rand(documents, generator=g) * 10 + 5 for p in pairs}
+    spread = 10.0 if trial % 3 == 0 else 8.5   # every third case gives the transfers no edge
+    confirmation = {p: torch.rand(documents, generator=g) * (10.0 if p == (0, 0) else spread) + 5 for p in pairs}
+    fit_counts = (torch.rand(documents, generator=g) > 0.1).long()
+    confirmation_counts = (torch.rand(documents, generator=g) > (0.7 if trial == 5 else 0.2)).long()
+    return {"pairs": pairs, "fit": fit, "confirmation": confirmation, "fit_counts": fit_counts,
+            "confirmation_counts": confirmation_counts, "replicates": 300 + 100 * trial}
+
+
+# ---- tile error surfaces / high-rate allocation cases ---------------------------------------------
+def allocation_inputs(seed: int = 515, k: int = 256, n: int = 384):
+    """Seeded regularised reference / reconstruction, dense covariance and scale vectors (CPU)."""
+
+    g = torch.Generator().manual_seed(seed)
+    reference = torch.randn((k, n), generator=g)
+    reconstruction = reference + 0.05 * torch.randn((k, n), generator=g)
+    x = torch.randn((4 * k, k), generator=g) * torch.exp(0.5 * torch.randn(k, generator=g))
+    hessian = (x.T @ x / (4 * k)).float()
+    suh = (torch.rand(k, generator=g) + 0.5) * torch.sign(torch.randn(k, generator=g))
+    svh = (torch.rand(n, generator=g) + 0.5) * torch.sign(torch.randn(n, generator=g))
+    return reference, reconstruction, hessian, suh, svh
+
+
+def allocation_cost_surfaces(axis: str, seed: int = 99):
+    """Two K2/K3/K4 cost surfaces on the Kimi-K3 tile grid (float64, CPU)."""
+
+    g = torch.Generator().manual_seed(seed + (axis == "n"))
+    grid = (192, 224) if axis == "k" else (224, 192)
+    gain = {2: 1.3, 3: 1.0, 4: 0.8}
+    return [{b: torch.rand(grid, generator=g, dtype=torch.float64) * gain[b] for b in (2, 3, 4)} for _ in range(2)]

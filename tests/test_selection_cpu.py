@@ -110,3 +110,103 @@ def test_single_process_gather_needs_no_process_group():
     local = torch.ones((2, 3, 2), dtype=torch.float64)
     full = selection.gather_candidate_table(local, [1, 3], 4)
     assert bool(torch.isnan(full[0]).all()) and bool((full[1] == 1).all()) and bool((full[3] == 1).all())
+
+
+# ---- phase-1 selection with the bootstrap gate, coupled-mode selection -----------------------------
+
+def _selection_golden():
+    import json
+    from pathlib import Path
+
+    return json.loads((Path(__file__).parent / "golden" / "selection_golden.json").read_text())
+
+
+def test_phase1_selection_matches_reference_decisions_and_intervals():
+    """Decisions, reasons and bootstrap intervals equal the reference's own
+    (tests/golden/selection_golden.json, made by tests/golden/make_selection_golden.py)."""
+
+    from dataclasses import asdict
+
+    from tests.helpers import COUPLED_MODE_CASE, phase1_case
+
+    gold = _selection_golden()
+
+    def same(got: dict, want: dict) -> None:
+        got = dict(got)
+        got["confirmation_ci95"] = list(got["confirmation_ci95"])
+        assert got == want
+
+    for trial in range(8):
+        case = phase1_case(trial)
+        pair = selection.select_phase1_rate_pair(
+            case["fit"], case["confirmation"], fit_counts=case["fit_counts"],
+            confirmation_counts=case["confirmation_counts"], modes=case["pairs"],
+            bootstrap_replicates=case["replicates"], seed=trial)
+        same(asdict(pair), gold["pair"][trial])
+        fit = {m: case["fit"][(m, 0)] for m in (0, 1, 2)}
+        confirmation = {m: case["confirmation"][(m, 0)] for m in (0, 1, 2)}
+        mode = selection.select_phase1_mode(
+            fit, confirmation, fit_counts=case["fit_counts"], confirmation_counts=case["confirmation_counts"],
+            bootstrap_replicates=case["replicates"], seed=trial)
+        same(asdict(mode), gold["mode"][trial])
+    assert selection.select_coupled_modes(*COUPLED_MODE_CASE) == gold["coupled"]
+
+
+def test_phase1_rate_pair_gate_and_support_rules():
+    """The scenarios of the reference's tests/test_qsrt_candidates.py:500-612."""
+
+    pairs = tuple((a, b) for a in (0, 1, 2) for b in (0, 1, 2))
+    ones = torch.ones(8, dtype=torch.int64)
+    fit = {p: torch.full((8,), 10.0 + p[0] + p[1]) for p in pairs}       # the fit fold prefers R0/R0 ...
+    confirmation = {p: torch.full((8,), 10.0) for p in pairs}
+    confirmation[(2, 1)] = torch.full((8,), 7.0)                         # ... the confirmation fold does not
+    chosen = selection.select_phase1_rate_pair(fit, confirmation, fit_counts=ones, confirmation_counts=ones,
+                                               modes=pairs, bootstrap_replicates=200, seed=7)
+    assert chosen.proposed == (2, 1) and chosen.selected == (2, 1) and chosen.accepted
+    assert chosen.confirmation_ci95[0] > 0
+
+    two = ((0, 0), (0, 1))
+    flat = {p: torch.ones(6) for p in two}
+    weak = selection.select_phase1_rate_pair(flat, flat, fit_counts=torch.ones(6, dtype=torch.int64),
+                                             confirmation_counts=torch.ones(3, dtype=torch.int64), modes=two,
+                                             min_fit_documents=4, min_confirmation_documents=4,
+                                             bootstrap_replicates=200)
+    assert weak.selected == (0, 0) and weak.reason == "insufficient confirmation-document support"
+
+    fit_m = {0: torch.full((8,), 10.0), 1: torch.full((8,), 10.5), 2: torch.full((8,), 8.0)}
+    conf_m = {0: torch.full((6,), 10.0), 1: torch.full((6,), 10.5), 2: torch.full((6,), 8.0)}
+    kwargs = dict(fit_counts=ones, confirmation_counts=torch.ones(6, dtype=torch.int64), mode_ids=(0, 1, 2),
+                  bootstrap_replicates=200, seed=7)
+    assert selection.select_phase1_mode(fit_m, conf_m, **kwargs).selected_r == 2
+    conf_m[2] = torch.full((6,), 12.0)
+    rejected = selection.select_phase1_mode(fit_m, conf_m, **kwargs)
+    assert rejected.proposed_r == 2 and rejected.selected_r == 0 and not rejected.accepted
+    few = selection.select_phase1_mode({m: torch.ones(5) for m in (0, 1)}, {m: torch.ones(5) for m in (0, 1)},
+                                       fit_counts=torch.ones(5, dtype=torch.int64),
+                                       confirmation_counts=torch.ones(5, dtype=torch.int64), mode_ids=(0, 1),
+                                       bootstrap_replicates=200)
+    assert few.selected_r == 0 and few.reason == "insufficient fit-document support"
+
+    with pytest.raises(ValueError, match="begin with R0/R0"):
+        selection.select_phase1_rate_pair(flat, flat, fit_counts=ones[:6], confirmation_counts=ones[:6],
+                                          modes=((0, 1), (0, 0)))
+    with pytest.raises(ValueError, match="at least 100"):
+        selection.bootstrap_improvement(torch.ones(4), torch.ones(4), torch.ones(4, dtype=torch.bool),
+                                        replicates=10, seed=0)
+    assert selection.bootstrap_improvement(torch.zeros(4), torch.ones(4), torch.ones(4, dtype=torch.bool),
+                                           replicates=100, seed=0) == (None, (None, None), 0)
+
+
+def test_coupled_mode_selection_rules():
+    sse = {"w1": {0: 3.0, 1: 2.0}, "w3": {0: 3.0, 1: 2.5}, "w2": {0: 1.0, 1: 1.0}}
+    picked = selection.select_coupled_modes(sse, {"r13": ("w1", "w3"), "r2": ("w2",)})
+    assert picked["r13"]["selected_mode"] == 1 and picked["r2"]["selected_mode"] == 0   # tie -> lower mode
+    assert picked["r13"]["sse_by_mode"] == {"R0": 6.0, "R1": 4.5}
+    with pytest.raises(ValueError, match="partition"):
+        selection.select_coupled_modes(sse, {"r13": ("w1", "w3")})
+    with pytest.raises(ValueError, match="share one mode ladder"):
+        selection.select_coupled_modes({"w1": {0: 1.0}, "w3": {0: 1.0, 1: 2.0}}, {"r13": ("w1", "w3")})
+    with pytest.raises(KeyError):
+        selection.select_coupled_modes(sse, {"r13": ("w1", "w9"), "r2": ("w2",)})
+    with pytest.raises(ValueError, match="finite and nonnegative"):
+        selection.select_coupled_modes({"w2": {0: -1.0}}, {"r2": ("w2",)})
