@@ -248,3 +248,99 @@ def adaptive_identity_shrinkage(local_covariance: torch.Tensor, weights: torch.T
         "max_local_alpha": max_local_alpha,
         "identity_scale": identity_scale,
     }
+
+
+PHASE1_H13_EXPERT_LOCAL_ALPHA = 0.0
+PHASE1_H2_EXPERT_LOCAL_ALPHA = 0.75
+PHASE1_H2_SHRINKAGE_POLICY = "weighted_oas_scaled_identity"
+
+
+def routed_input_hessian(values: torch.Tensor, route_weights: torch.Tensor, *, identity_shrinkage: float,
+                         device: torch.device | None = None) -> tuple[torch.Tensor, dict[str, float]]:
+    """Route-weighted covariance ``Σ w² x xᵀ / Σ w²`` blended with ``identity_shrinkage`` of its mean
+    diagonal (qsrt/glm52_routed_input_curvature.py:76-109).  The contraction is the same weighted
+    SYRK kernel as ``weighted_covariance`` with ``w²`` as row weights."""
+
+    if values.ndim != 2 or route_weights.ndim != 1:
+        raise ValueError("curvature values must be a matrix with one weight per row")
+    if route_weights.numel() != values.shape[0]:
+        raise ValueError("curvature route weights do not match the row count")
+    if not math.isfinite(identity_shrinkage) or not 0.0 < identity_shrinkage <= 1.0:
+        raise ValueError("identity_shrinkage must be in (0, 1]")
+    device = torch.device(device) if device is not None else values.device
+    if device.type != "cuda":
+        raise ValueError("the B200 Hessian path requires a CUDA device")
+    weights = route_weights.to(device=device, dtype=torch.float32).clamp_min(0.0)
+    squared = weights.square()
+    mass = float(squared.sum().item())
+    if mass <= 0.0:
+        raise ValueError("curvature route weights have zero squared mass")
+    dimension = int(values.shape[1])
+    accumulator = torch.empty((dimension, dimension), dtype=torch.float32, device=device)
+    step = accumulate_hessian_tensor_cores if (
+        USE_TENSOR_CORES and dimension % 128 == 0 and tensor_cores_available()) else accumulate_hessian
+    step(accumulator, values.to(device=device, dtype=torch.float32), squared, accumulate=False)
+    hessian = finish_hessian(accumulator, mass)
+    diagonal_mean = float(hessian.diagonal().mean().item())
+    if not math.isfinite(diagonal_mean) or diagonal_mean <= 0.0:
+        raise ValueError("curvature covariance has a nonpositive mean diagonal")
+    hessian.mul_(1.0 - identity_shrinkage)
+    hessian.diagonal().add_(identity_shrinkage * diagonal_mean)
+    return hessian.contiguous(), {
+        "row_count": int(values.shape[0]),
+        "squared_route_mass": mass,
+        "unshrunk_diagonal_mean": diagonal_mean,
+        "identity_shrinkage": float(identity_shrinkage),
+    }
+
+
+def build_expert_hessians(inputs: torch.Tensor, gates: torch.Tensor, source_middle: torch.Tensor, *,
+                          global_h13: torch.Tensor, global_h2: torch.Tensor, device: torch.device,
+                          h13_alpha: float = PHASE1_H13_EXPERT_LOCAL_ALPHA, h2_alpha: float | None = None,
+                          chunk_rows: int = 256) -> tuple[torch.Tensor, torch.Tensor, dict]:
+    """H13 and a support-aware post-activation H2 for one expert (qsrt/qsrt_candidates.py:534-618).
+
+    Row weights are ``gate²``.  H13 is the global covariance, optionally blended with the expert's
+    own; H2 is the expert's covariance of ``source_middle`` shrunk toward its trace-scaled identity,
+    by weighted OAS (capped at 0.75) unless a fixed ``h2_alpha`` is given.  ``global_h2`` only fixes
+    the dimension.  ``chunk_rows`` is accepted for compatibility: the kernels stream all rows.
+    """
+
+    if inputs.ndim != 2 or inputs.shape[0] != gates.shape[0]:
+        raise ValueError("invalid expert input covariance samples")
+    if source_middle.ndim != 2 or source_middle.shape[0] != inputs.shape[0]:
+        raise ValueError("source middle rows do not match expert inputs")
+    device = torch.device(device)
+    global_h13 = global_h13.to(device=device, dtype=torch.float32)
+    if global_h2.shape != (source_middle.shape[1], source_middle.shape[1]):
+        raise ValueError("global H2 dimension does not match source middle rows")
+    weights = gates.float().square()
+    if h13_alpha == 0.0:
+        h13, h13_weight = global_h13, float(weights.double().sum())
+    else:
+        local_h13, h13_weight = weighted_covariance(inputs, weights, device=device, return_cpu=False)
+        h13 = shrink_covariance(global_h13, local_h13, h13_alpha)
+    local_h2, h2_weight = weighted_covariance(source_middle, weights, device=device, return_cpu=False)
+    if not math.isclose(h13_weight, h2_weight, rel_tol=1e-9, abs_tol=1e-12):
+        raise ValueError("H13 and H2 expert covariance weights differ")
+    if h2_alpha is None:
+        h2, info = adaptive_identity_shrinkage(local_h2, weights, max_local_alpha=PHASE1_H2_EXPERT_LOCAL_ALPHA)
+        evidence = {
+            "h2_shrinkage_policy": PHASE1_H2_SHRINKAGE_POLICY,
+            "h2_local_alpha": info["local_alpha"],
+            "h2_local_alpha_cap": info["max_local_alpha"],
+            "h2_effective_sample_size": info["effective_sample_size"],
+            "h2_oas_shrinkage": info["oas_shrinkage"],
+            "h2_identity_scale": info["identity_scale"],
+        }
+    else:
+        identity_scale = float(torch.trace(local_h2) / local_h2.shape[0])
+        prior = torch.eye(local_h2.shape[0], dtype=torch.float32, device=device).mul_(identity_scale)
+        h2 = shrink_covariance(prior, local_h2, h2_alpha)
+        evidence = {
+            "h2_shrinkage_policy": "fixed_alpha_scaled_identity",
+            "h2_local_alpha": float(h2_alpha),
+            "h2_local_alpha_cap": float(h2_alpha),
+            "h2_identity_scale": identity_scale,
+        }
+    return h13, h2, {"gate_square_sum": h13_weight, "h13_local_alpha": float(h13_alpha), **evidence}

@@ -177,3 +177,21 @@ def allocation_cost_surfaces(axis: str, seed: int = 99):
     grid = (192, 224) if axis == "k" else (224, 192)
     gain = {2: 1.3, 3: 1.0, 4: 0.8}
     return [{b: torch.rand(grid, generator=g, dtype=torch.float64) * gain[b] for b in (2, 3, 4)} for _ in range(2)]
+
+
+# ---- per-expert Hessian construction cases --------------------------------------------------------
+def expert_hessian_inputs(seed: int = 2718, tokens: int = 640, hidden: int = 256, middle: int = 128):
+    """Seeded routed inputs, gates, post-activation rows and global covariances (CPU float32)."""
+
+    g = torch.Generator().manual_seed(seed)
+    scale = torch.exp(0.4 * torch.randn(hidden, generator=g))
+    inputs = torch.randn((tokens, hidden), generator=g) * scale
+    gates = torch.rand(tokens, generator=g) * 0.6 + 0.02
+    gates[::17] = 0.0
+    source_middle = torch.randn((tokens, middle), generator=g) * torch.exp(0.3 * torch.randn(middle, generator=g))
+    base = torch.randn((4 * hidden, hidden), generator=g) * scale
+    global_h13 = (base.T @ base / (4 * hidden)).float()
+    global_h2 = torch.eye(middle)
+    route_weights = gates.clone()
+    route_weights[5::29] = -0.3   # negative route weights are clamped to zero
+    return inputs, gates, source_middle, global_h13, global_h2, route_weights

@@ -262,3 +262,94 @@ def test_tensor_core_wait_expiry_is_reported_and_harmless(cuda_device):
     cov, _ = hessian.weighted_covariance(x, w, device=cuda_device, tensor_cores=True)
     ref = (x.double().T * w.double()) @ x.double() / w.double().sum()
     assert _rel_fro(cov, ref) < 1e-5
+
+
+# ---- named per-expert constructors against reference-made goldens ----------------------------------
+def _hessian_golden():
+    from pathlib import Path
+
+    return np.load(Path(__file__).parent / "golden" / "hessian_golden.npz")
+
+
+@pytest.mark.parametrize("tensor_cores", [True, False])
+@pytest.mark.parametrize("name,kwargs", [("default", {}), ("blend", {"h13_alpha": 0.25}),
+                                         ("fixed", {"h13_alpha": 0.25, "h2_alpha": 0.4})])
+def test_build_expert_hessians_matches_reference(cuda_device, monkeypatch, tensor_cores, name, kwargs):
+    """qsrt/qsrt_candidates.py:534-618 run by the reference on the CPU vs both device kernels."""
+
+    from tests.helpers import expert_hessian_inputs
+
+    monkeypatch.setattr(hessian, "USE_TENSOR_CORES", tensor_cores)
+    golden = _hessian_golden()
+    inputs, gates, middle, global_h13, global_h2, _ = expert_hessian_inputs()
+    h13, h2, evidence = hessian.build_expert_hessians(inputs, gates, middle, global_h13=global_h13,
+                                                      global_h2=global_h2, device=cuda_device, **kwargs)
+    assert h13.is_cuda and h2.is_cuda
+    if name == "default":
+        assert torch.equal(h13.cpu(), global_h13)
+    else:
+        assert _rel_fro(h13.cpu(), torch.from_numpy(golden["blend_h13"])) < 1e-5
+    assert _rel_fro(h2.cpu(), torch.from_numpy(golden[f"{name}_h2"])) < 1e-5
+    assert torch.equal(h2, h2.T)
+    assert evidence["h2_shrinkage_policy"] == str(golden[f"{name}_policy"])
+    for key, value in evidence.items():
+        if key == "h2_shrinkage_policy":
+            continue
+        want = float(golden[f"{name}_{key}"])
+        assert abs(value - want) <= 2e-6 * max(1.0, abs(want)), key
+    assert set(evidence) == {k[len(name) + 1:] for k in golden.files if k.startswith(name + "_")
+                             and not k.endswith(("_h13", "_h2"))} - {"policy"} | {"h2_shrinkage_policy"}
+
+
+def test_build_expert_hessians_errors(cuda_device):
+    from tests.helpers import expert_hessian_inputs
+
+    inputs, gates, middle, global_h13, global_h2, _ = expert_hessian_inputs()
+    common = dict(global_h13=global_h13, global_h2=global_h2, device=cuda_device)
+    with pytest.raises(ValueError, match="invalid expert input covariance samples"):
+        hessian.build_expert_hessians(inputs, gates[:-1], middle, **common)
+    with pytest.raises(ValueError, match="source middle rows do not match"):
+        hessian.build_expert_hessians(inputs, gates, middle[:-1], **common)
+    with pytest.raises(ValueError, match="global H2 dimension"):
+        hessian.build_expert_hessians(inputs, gates, middle, global_h13=global_h13,
+                                      global_h2=torch.eye(64), device=cuda_device)
+    with pytest.raises(ValueError):
+        hessian.build_expert_hessians(inputs, torch.zeros_like(gates), middle, **common)
+
+
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_routed_input_hessian_matches_reference(cuda_device, monkeypatch, tensor_cores):
+    """qsrt/glm52_routed_input_curvature.py:76-109 run by the reference on the CPU."""
+
+    from tests.helpers import expert_hessian_inputs
+
+    monkeypatch.setattr(hessian, "USE_TENSOR_CORES", tensor_cores)
+    golden = _hessian_golden()
+    inputs, _, _, _, _, route_weights = expert_hessian_inputs()
+    got, stats = hessian.routed_input_hessian(inputs.to(cuda_device), route_weights, identity_shrinkage=0.10)
+    assert _rel_fro(got.cpu(), torch.from_numpy(golden["routed_010_hessian"])) < 1e-5
+    assert torch.equal(got, got.T)
+    assert stats["row_count"] == int(golden["routed_010_row_count"])
+    for key in ("squared_route_mass", "unshrunk_diagonal_mean", "identity_shrinkage"):
+        want = float(golden[f"routed_010_{key}"])
+        assert abs(stats[key] - want) <= 2e-6 * abs(want), key
+    full, stats = hessian.routed_input_hessian(inputs, route_weights, identity_shrinkage=1.0, device=cuda_device)
+    diagonal = torch.from_numpy(golden["routed_100_diagonal"])
+    assert torch.count_nonzero(full - torch.diag(full.diagonal())) == 0
+    assert _rel_fro(full.diagonal().cpu(), diagonal) < 2e-6
+
+
+def test_routed_input_hessian_errors(cuda_device):
+    x = torch.randn(8, 64, device=cuda_device)
+    w = torch.rand(8, device=cuda_device)
+    with pytest.raises(ValueError, match="one weight per row"):
+        hessian.routed_input_hessian(x[0], w, identity_shrinkage=0.1)
+    with pytest.raises(ValueError, match="do not match the row count"):
+        hessian.routed_input_hessian(x, w[:-1], identity_shrinkage=0.1)
+    for bad in (0.0, 1.5, float("nan")):
+        with pytest.raises(ValueError, match=r"identity_shrinkage must be in \(0, 1\]"):
+            hessian.routed_input_hessian(x, w, identity_shrinkage=bad)
+    with pytest.raises(ValueError, match="zero squared mass"):
+        hessian.routed_input_hessian(x, -w, identity_shrinkage=0.1)
+    with pytest.raises(ValueError, match="nonpositive mean diagonal"):
+        hessian.routed_input_hessian(torch.zeros_like(x), w, identity_shrinkage=0.1)

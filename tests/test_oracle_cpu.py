@@ -121,3 +121,40 @@ def test_cpu_restatement_full_context_rows(bits):
     pick = np.r_[1, 9, 17, 25, 32, 33, 35]
     _, states = oracle.quantize_tiles(tiles[pick], oracle.sqg_xor_cheb_t12_bytes(bits), bits, 128)
     assert np.array_equal(states, golden[f"states_k{bits}_c128"][pick])
+
+
+# ---- Hessian constructors: float64 restatement vs matrices the reference produced ------------------
+def _rel_fro(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.mark.parametrize("name,kwargs", [("default", {}), ("blend", {"h13_alpha": 0.25}),
+                                         ("fixed", {"h13_alpha": 0.25, "h2_alpha": 0.4})])
+def test_hessian_oracle_matches_reference_made_golden(name, kwargs):
+    from oracle import hessian_oracle
+
+    golden = np.load(Path(__file__).parent / "golden" / "hessian_golden.npz")
+    inputs, gates, middle, global_h13, _, _ = helpers.expert_hessian_inputs()
+    h13, h2, evidence = hessian_oracle.build_expert_hessians(
+        inputs.numpy(), gates.numpy(), middle.numpy(), global_h13.numpy(), **kwargs)
+    if name != "default":
+        assert _rel_fro(h13, golden["blend_h13"]) < 1e-5
+    assert _rel_fro(h2, golden[f"{name}_h2"]) < 1e-5
+    for key, value in evidence.items():
+        want = float(golden[f"{name}_{key}"])
+        assert abs(value - want) <= 2e-6 * max(1.0, abs(want)), key
+
+
+def test_routed_hessian_oracle_matches_reference_made_golden():
+    from oracle import hessian_oracle
+
+    golden = np.load(Path(__file__).parent / "golden" / "hessian_golden.npz")
+    inputs, _, _, _, _, route_weights = helpers.expert_hessian_inputs()
+    hessian, stats = hessian_oracle.routed_input_hessian(inputs.numpy(), route_weights.numpy(), 0.10)
+    assert _rel_fro(hessian, golden["routed_010_hessian"]) < 1e-5
+    for key, value in stats.items():
+        want = float(golden[f"routed_010_{key}"])
+        assert abs(value - want) <= 2e-6 * abs(want), key
+    full, _ = hessian_oracle.routed_input_hessian(inputs.numpy(), route_weights.numpy(), 1.0)
+    assert _rel_fro(np.diagonal(full), golden["routed_100_diagonal"]) < 2e-6
