@@ -218,6 +218,30 @@ int qsrtb_hessian_tc_wait_probe(int* status_flag, void* stream);
 int qsrtb_tile_reduce(const float* a, const float* b, int rows, int cols, int lda, int ldb, int mode,
                       double* out, void* stream);
 
+/* ---- (f)3: dense-H path refinement, scoring and acceptance for one 16-row block -------------
+ * Replaces the per-block tail of refine_h2_viterbi_paths (qsrt/h2_viterbi_refine.py:451-505;
+ * _conditional_scores :261-279).  All row pointers address the FIRST of the block's 16 rows.
+ *   weight, target : float32 [16, n] regularised weights and the conditional target (cast to
+ *                    float32, as the reference casts it before the tile search).
+ *   recon, states  : stored reconstruction rows [16, n] and payload [n/16, 256]; rewritten for
+ *                    accepted tiles.
+ *   cand, cand_states : `variants` proposals, [variants, 16, n] (pitches ldc, cand_stride) and
+ *                    [variants, n/16, 256] (pitch cand_state_stride), as written by
+ *                    qsrtb_ldlq_quantize_rows with batch = variants.
+ *   h_block        : the block's 16x16 diagonal Hessian block; col_weights [n]; err [16, n]
+ *                    (weight - recon, updated); delta [16, n] receives new err - old err (0 for
+ *                    kept tiles).  These four are float32, or float64 when score_is_double.
+ *   A tile switches to its first best-scoring proposal when
+ *   best + abs_tol + rel_tol * |current| < current.
+ *   counters[0] += accepted tiles, counters[1] += distinct payloads per tile (device words).
+ */
+int qsrtb_refine_select(const float* weight, int ldw, const float* target, int ldt, float* recon,
+                        int ldq, int n, const float* cand, int ldc, int64_t cand_stride,
+                        int variants, const int16_t* cand_states, int64_t cand_state_stride,
+                        int16_t* states, const void* h_block, int ldh, const void* col_weights,
+                        void* err, int lde, void* delta, int ldd, double abs_tol, double rel_tol,
+                        int score_is_double, unsigned long long* counters, void* stream);
+
 /* ---- P1: bit packer --------------------------------------------------------------------
  * Replaces pack_trellis (qsrt/exl3_encoder_backend.py:2361-2372, third-party
  * ext.pack_trellis) and its torch restatement pack_trellis_edges (qsrt/qsrt.py:861-883).

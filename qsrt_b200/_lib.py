@@ -70,6 +70,12 @@ _SIGNATURES = {
     "qsrtb_pack_trellis": (_c.c_int, [_PTR, _c.c_int64, _c.c_int, _PTR, _PTR]),
     "qsrtb_mxfp4_dequant": (_c.c_int, [_PTR, _PTR, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR]),
     "qsrtb_tile_reduce": (_c.c_int, [_PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR]),
+    "qsrtb_refine_select": (
+        _c.c_int,
+        [_PTR, _c.c_int, _PTR, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int64, _c.c_int,
+         _PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _PTR, _PTR, _c.c_int, _PTR, _c.c_int, _c.c_double,
+         _c.c_double, _c.c_int, _PTR, _PTR],
+    ),
     "qsrtb_pack_records": (
         _c.c_int,
         [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _c.c_int64,

@@ -15,7 +15,8 @@ import json
 
 import torch
 
-from . import allocation, codec, coupled, encoder, hessian, mxfp4, records, storage, tables
+from . import allocation, codec, coupled, encoder, hessian, mxfp4, records, refine, storage, tables
+from . import tiles as tile_search
 
 
 _flush = None
@@ -110,7 +111,25 @@ def main() -> None:
     mx_scale = torch.randint(110, 130, (mx_rows, mx_cols // 32), device=dev, dtype=torch.uint8, generator=g)
     mx_bytes = mx_rows * mx_cols * 4 + mx_packed.numel() + mx_scale.numel()
     w_other = torch.randn((k, n), device=dev, generator=g)
+    # dense-H path refinement of one down projection in encoder orientation [2048, 7168], K3
+    rf_rows, rf_cols = 2048, 7168
+    rf_weight = torch.randn((rf_rows, rf_cols), device=dev, generator=g)
+    rf_x = torch.randn((4 * rf_rows, rf_rows), device=dev, generator=g)
+    rf_hessian = (rf_x.T @ rf_x) / rf_x.shape[0]
+    rf_hessian.diagonal().add_(0.025)
+    rf_args = {"K": 3, "devices": [str(dev)], "tailbite_context": 128, "sqg_e4m3_lut": tables.sqg_xor_cheb_t12_bytes(3)}
+    rf_order = encoder.tensor_core_perm(dev)
+    rf_tiles = rf_weight.reshape(rf_rows // 16, 16, rf_cols // 16, 16).permute(0, 2, 1, 3).reshape(-1, 256)
+    rf_recon, rf_states = tile_search.quantize_tiles(rf_tiles[:, rf_order].contiguous(), rf_args)
+    rf_q = rf_recon[:, torch.argsort(rf_order)].reshape(rf_rows // 16, rf_cols // 16, 16, 16).permute(0, 2, 1, 3)
+    rf_q = rf_q.reshape(rf_rows, rf_cols).contiguous()
+    rf_states = rf_states.reshape(rf_rows // 16, rf_cols // 16, 256)
+    rf_config = refine.H2ViterbiRefineConfig(sweeps=1)
+    del rf_x, rf_tiles, rf_recon
     cases = {
+        "refine_h2_viterbi_paths, one sweep [2048, 7168] K3 (128 row blocks of 448 tiles)":
+            (lambda: refine.refine_h2_viterbi_paths(rf_weight, rf_hessian, rf_q, rf_states, rf_args, rf_config),
+             (rf_rows // 16) * (rf_cols // 16), "T"),
         "tile_squared_error": (lambda: allocation.tile_squared_error(w, w_other), 8 * k * n + k * n // 32, "B"),
         "mxfp4_dequant [out, in]": (lambda: mxfp4.dequant(mx_packed, mx_scale), mx_bytes, "B"),
         "mxfp4_dequant -> encoder orientation [in, out]":
@@ -154,8 +173,17 @@ def main() -> None:
         ms = _time(fn, args.iters)
         rate = work / (ms * 1e-3)
         line = {"kernel": name, "ms": ms, "work_per_launch": work}
+        if kind == "T":
+            # share of the call spent inside the tile-search launches (events on the launching stream)
+            tile_search.search_timings = []
+            fn()
+            torch.cuda.synchronize()
+            line["tile_search_ms"] = sum(a.elapsed_time(b) for a, b, _, _ in tile_search.search_timings)
+            tile_search.search_timings = None
         if kind == "B":
             line["GB_per_s"] = rate / 1e9
+        elif kind == "T":
+            line["tiles_per_s"] = rate
         else:
             line["TFLOP_per_s"] = rate / 1e12
         print(json.dumps(line), flush=True)

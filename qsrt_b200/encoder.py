@@ -872,8 +872,12 @@ def _reject_out_of_scope(quant_args: dict) -> None:
     for key, what in _OUT_OF_SCOPE_ARGS.items():
         if quant_args.get(key):
             raise NotImplementedError(f"{what} is a research arm outside the B200 encoder hot path")
-    if int(quant_args.get("h2_viterbi_refine_sweeps", 0) or 0) > 0:
-        raise NotImplementedError("dense-H path refinement sweeps are not part of the B200 hot path yet")
+
+
+def _refine():
+    from . import refine  # late: refine reaches back into this module for the row kernel
+
+    return refine
 
 
 def _deregularize(weight_q: torch.Tensor, su: torch.Tensor, sv: torch.Tensor) -> torch.Tensor:
@@ -930,7 +934,9 @@ def quantize_qsrt(weight: torch.Tensor, H_data: dict, quant_args: dict, return_w
         else:
             weight_q, encoded_q = ldlq(weight_r, L, quant_args)
         del L
-        quant_args["h2_viterbi_refine_receipt"] = {"enabled": False, "reason": "disabled", "sweeps": []}
+        # dense-H path refinement of the finished candidate (exl3_encoder_backend.py:2970-2979)
+        weight_q, encoded_q, quant_args["h2_viterbi_refine_receipt"] = _refine().refine_uniform_h2_candidate(
+            weight_r, H, weight_q, encoded_q, quant_args)
     else:
         if mixed_rate:
             raise ValueError("variable-rate quantization requires a non-fallback dense Hessian")
@@ -993,6 +999,9 @@ def _uniform_prepare(weights, H_datas, quant_args_list, verbose):
         raise ValueError("mixed-rate LDLQ is currently supported by quantize_qsrt, not the same-K batch API")
     for qa in quant_args_list:
         _reject_out_of_scope(qa)
+        if int(qa.get("h2_viterbi_refine_sweeps", 0) or 0) > 0:
+            raise NotImplementedError("dense-H path refinement runs in quantize_qsrt and quantize_qsrt_batch, "
+                                      "not in the same-K batch API")
     n_t = len(weights)
     qa0 = quant_args_list[0]
     device = torch.device(qa0["devices"][0])
@@ -1204,7 +1213,9 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
     for (source, candidate), (weight_q, encoded) in zip(members, encoded_all):
         item = prepared[source]
         args = quant_args_groups[source][candidate]
-        weight_q, encoded = weight_q[0], encoded[0]
+        # dense-H path refinement per finished candidate (exl3_encoder_backend.py:3296-3312)
+        weight_q, encoded, receipt = _refine().refine_uniform_h2_candidate(
+            item["weight_r"], item["H"], weight_q[0], encoded[0], args)
         numerator = block_trace(item["weight_r"] - weight_q, item["H"])
         if "suh" not in item:
             item["suh"] = item["su"].flatten().contiguous().to(dtype=torch.half, copy=True)
@@ -1221,7 +1232,7 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
             "svh": item["svh"],
             "proxy": numerator / max(denominators[source], 1e-8),
             "g_scale": item["g_scale"],
-            "h2_viterbi_refine": {"enabled": False, "reason": "disabled", "sweeps": []},
+            "h2_viterbi_refine": receipt,
         })
     return results
 

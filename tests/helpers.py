@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import importlib.util
+import math
 import sys
 from functools import lru_cache
 from pathlib import Path
@@ -195,3 +196,44 @@ def expert_hessian_inputs(seed: int = 2718, tokens: int = 640, hidden: int = 256
     route_weights = gates.clone()
     route_weights[5::29] = -0.3   # negative route weights are clamped to zero
     return inputs, gates, source_middle, global_h13, global_h2, route_weights
+
+
+# ---- dense-H path refinement cases ----------------------------------------------------------------
+def spd_hessian(size: int, condition: float, seed: int) -> torch.Tensor:
+    """Seeded SPD matrix with log-spaced spectrum, unit mean diagonal (float32, CPU)."""
+
+    g = torch.Generator().manual_seed(seed)
+    basis, _ = torch.linalg.qr(torch.randn((size, size), generator=g, dtype=torch.float64))
+    half = 0.5 * math.log(condition)
+    spectrum = torch.exp(torch.linspace(-half, half, size, dtype=torch.float64))
+    h = (basis * spectrum) @ basis.T + 0.025 * torch.eye(size, dtype=torch.float64)
+    return (h / h.diagonal().mean()).float()
+
+
+REFINE_CASES = {
+    # name: (bits, rows, columns, condition, sweeps, column weights?, guidance strength, fp64 score?)
+    "k3_plain": (3, 64, 96, 30.0, 2, False, 0.0, False),
+    "k2_weighted_guided_fp64": (2, 48, 64, 12.0, 2, True, 0.5, True),
+}
+
+
+def refine_case_inputs(name: str):
+    """Seeded weight, Hessian, column weights and guidance tensors of one refinement case (CPU)."""
+
+    bits, rows, columns, condition, sweeps, weighted, strength, fp64 = REFINE_CASES[name]
+    seed = 1000 + 17 * bits + rows
+    g = torch.Generator().manual_seed(seed)
+    weight = 1.2 * torch.randn((rows, columns), generator=g)
+    hessian = spd_hessian(rows, condition, seed + 1)
+    column_weights = (0.5 + torch.rand(columns, generator=g)) if weighted else None
+    gradient = 0.05 * torch.randn((rows, columns), generator=g) if strength else None
+    return weight, hessian, column_weights, gradient
+
+
+def matrix_to_tc_tiles(matrix: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
+    rows, columns = matrix.shape
+    return matrix.reshape(rows // 16, 16, columns // 16, 16).permute(0, 2, 1, 3).reshape(-1, 256)[:, order]
+
+
+def tc_tiles_to_matrix(tiles: torch.Tensor, inverse: torch.Tensor, rows: int, columns: int) -> torch.Tensor:
+    return tiles[:, inverse].reshape(rows // 16, columns // 16, 16, 16).permute(0, 2, 1, 3).reshape(rows, columns)
