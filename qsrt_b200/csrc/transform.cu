@@ -228,8 +228,8 @@ __global__ void col_sumsq_fold_kernel(const float* __restrict__ partial, int col
 // them become zero (identity blocks whose main diagonal is then cleared).  Three launches:
 //   inverse : one warp per diagonal block inverts it by forward substitution and parks the
 //             result in the tile to its right (above the diagonal: free until the last launch);
-//   apply   : grid.x = block column, grid.y = 256-row chunk below it; a thread multiplies its
-//             row's 16 values by the parked inverse;
+//   apply   : grid.x = group of 8 block columns, grid.y = 128-row chunk; every 16-value row piece
+//             below its diagonal block is multiplied by that block's parked inverse;
 //   zero    : diagonal blocks and everything above them, the parked inverses included.
 // The last block column has no rows below it and needs no inverse.
 __global__ void __launch_bounds__(32)
@@ -257,34 +257,54 @@ block_ldl_inverse_kernel(float* __restrict__ c, int ld)
     }
 }
 
+// 128 rows x 8 block columns (128 columns) per CTA.  A lane owns one float4 of a row: block column
+// lane/4, columns 4*(lane%4)..+3 of it, so a warp reads and writes 512 contiguous bytes of one row.
+// Its 64 inverse entries inv[k][4q..4q+3] stay in registers for all 16 rows the warp visits; the 16
+// inputs of a row piece come from the 4 lanes of the group by shuffle.  Sums run over k = 0..15 in
+// order, as a single thread per row piece would add them.
 __global__ void __launch_bounds__(256)
 block_ldl_apply_kernel(float* __restrict__ c, int n, int ld)
 {
-    __shared__ float inv[16][17];
-    const int d0 = blockIdx.x * 16;
-    const int t = threadIdx.x;
-    if (int(blockIdx.y) * 256 + 255 < d0 + 16) return;
-    inv[t >> 4][t & 15] = c[int64_t(d0 + (t >> 4)) * ld + d0 + 16 + (t & 15)];
-    __syncthreads();
-    const int r = blockIdx.y * 256 + t;
-    if (r >= n || r < d0 + 16) return;
-    float* row = c + int64_t(r) * ld + d0;
-    float in[16], out[16];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = blockIdx.x * 8 + (lane >> 2), q = lane & 3;
+    const int row_begin = blockIdx.y * 128;
+    if (row_begin + 127 < blockIdx.x * 128 + 16) return;   // nothing of this chunk lies below the group
+    const int d0 = b * 16;
+    const bool has_rows = d0 + 16 < n;                      // also excludes block columns past the end
+    float4 inv[16];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float4 q = reinterpret_cast<const float4*>(row)[k];
-        in[4 * k] = q.x; in[4 * k + 1] = q.y; in[4 * k + 2] = q.z; in[4 * k + 3] = q.w;
+    for (int k = 0; k < 16; ++k)
+        inv[k] = has_rows ? *reinterpret_cast<const float4*>(c + int64_t(d0 + k) * ld + d0 + 16 + 4 * q)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const int group = lane & ~3;
+    // eight rows per batch: all loads are issued before the first store of the batch, which the
+    // compiler cannot do by itself for loads and stores through the same array
+    for (int i0 = 0; i0 < 16; i0 += 8) {
+        float4 v[8];
+        bool active[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int r = row_begin + warp + 8 * (i0 + u);
+            active[u] = has_rows && r < n && r >= d0 + 16;
+            v[u] = active[u] ? *reinterpret_cast<const float4*>(c + int64_t(r) * ld + d0 + 4 * q)
+                             : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float4 out = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const float mine = (k & 3) == 0 ? v[u].x : (k & 3) == 1 ? v[u].y : (k & 3) == 2 ? v[u].z : v[u].w;
+                const float in = __shfl_sync(0xffffffffu, mine, group + (k >> 2));
+                out.x = fmaf(in, inv[k].x, out.x);
+                out.y = fmaf(in, inv[k].y, out.y);
+                out.z = fmaf(in, inv[k].z, out.z);
+                out.w = fmaf(in, inv[k].w, out.w);
+            }
+            const int r = row_begin + warp + 8 * (i0 + u);
+            if (active[u]) *reinterpret_cast<float4*>(c + int64_t(r) * ld + d0 + 4 * q) = out;
+        }
     }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        float s = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) s += in[k] * inv[k][j];
-        out[j] = s;
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        reinterpret_cast<float4*>(row)[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
 }
 
 // Zero the diagonal blocks and everything above them (row r, columns >= 16*floor(r/16)).
@@ -361,7 +381,7 @@ extern "C" int qsrtb_block_ldl_normalize(float* chol, int n, int ld, void* strea
     const int columns = n / 16 - 1;   // block columns with rows below them
     if (columns > 0) {
         block_ldl_inverse_kernel<<<columns, 32, 0, s>>>(chol, ld);
-        block_ldl_apply_kernel<<<dim3(columns, (n + 255) / 256), 256, 0, s>>>(chol, n, ld);
+        block_ldl_apply_kernel<<<dim3((n + 127) / 128, (n + 127) / 128), 256, 0, s>>>(chol, n, ld);
     }
     block_ldl_zero_upper_kernel<<<n, 256, 0, s>>>(chol, n, ld);
     const cudaError_t err = cudaGetLastError();
