@@ -115,6 +115,55 @@ unpack_decode_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int b
     }
 }
 
+// Labels only: 32 warps per SM share one staged copy of the table (one 1024-thread CTA per SM) and
+// every warp decodes two tiles per iteration, so two tiles' loads and their 16 table look-ups per
+// lane are in flight together; with one tile per warp the kernel waited on its own load latency.
+__global__ void __launch_bounds__(1024, 1)
+decode_e4m3_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int bits,
+                   const uint8_t* __restrict__ lut_state, uint8_t* __restrict__ out_e4m3)
+{
+    extern __shared__ __align__(16) uint8_t sh_lut[];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(lut_state);
+        for (int i = threadIdx.x; i < 4096; i += blockDim.x) reinterpret_cast<uint4*>(sh_lut)[i] = src[i];
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const int chunk_bits = 8 * bits, words_per_tile = 8 * bits;
+    const unsigned long long chunk_mask = (1ull << chunk_bits) - 1ull;
+    const int bit0 = lane * chunk_bits;
+    const int w = bit0 >> 5, off = bit0 & 31;
+    const int w_next = min(w + 1, words_per_tile - 1);
+    const int64_t warps = int64_t(gridDim.x) * 32;
+    const int64_t pairs = (n_tiles + 1) / 2;
+    for (int64_t pair = int64_t(blockIdx.x) * 32 + (threadIdx.x >> 5); pair < pairs; pair += warps) {
+        uint32_t w0[2], w1[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int64_t tile = 2 * pair + u;
+            live[u] = tile < n_tiles;
+            const uint32_t* words = packed + (live[u] ? tile : 0) * words_per_tile;
+            w0[u] = words[w];
+            w1[u] = words[w_next];
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned long long two = (static_cast<unsigned long long>(w0[u]) << 32) | w1[u];
+            const uint32_t chunk = uint32_t((two >> (64 - off - chunk_bits)) & chunk_mask);
+            const uint32_t prev = __shfl_sync(0xffffffffu, chunk, (lane + 31) & 31);
+            const unsigned long long window = (static_cast<unsigned long long>(prev) << chunk_bits) | chunk;
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo |= uint32_t(sh_lut[uint32_t(window >> ((7 - i) * bits)) & 0xffffu]) << (8 * i);
+                hi |= uint32_t(sh_lut[uint32_t(window >> ((3 - i) * bits)) & 0xffffu]) << (8 * i);
+            }
+            if (live[u]) reinterpret_cast<uint2*>(out_e4m3 + (2 * pair + u) * 256)[lane] = make_uint2(lo, hi);
+        }
+    }
+}
+
 // states [kt, nt, 256] (tensor-core order) -> row-major float32 [kt*16, nt*16].
 // One warp per tile.  Lane l holds tensor-core elements 8l..8l+7, i.e. rows {r0, r0+1, r0+8,
 // r0+9} x columns {c0, c0+8} with r0 = 2*(l%4), c0 = l/4 (exl3_encoder_backend.py:35-57): each
@@ -199,6 +248,18 @@ extern "C" int qsrtb_unpack_decode(const int16_t* packed, int64_t n_tiles, int b
     if (n_tiles == 0) return QSRTB_OK;
     if (!packed || (!out_states && !out_e4m3)) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
     if (out_e4m3 && !lut_state) return qsrtb_fail(QSRTB_EINVAL, "decoding needs the table");
+    if (out_e4m3 && !out_states) {
+        int device = 0, sms = 148;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        const int64_t wanted = (n_tiles + 63) / 64;   // 32 warps x 2 tiles per block and iteration
+        cudaFuncSetAttribute(decode_e4m3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+        decode_e4m3_kernel<<<int(wanted < sms ? wanted : sms), 1024, 65536, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const uint32_t*>(packed), n_tiles, bits, lut_state, out_e4m3);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return qsrtb_fail_cuda(e, "decode launch");
+        return QSRTB_OK;
+    }
     const size_t smem = out_e4m3 ? 65536 : 0;
     cudaFuncSetAttribute(unpack_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
     const int grid = out_e4m3 ? lut_grid(n_tiles) : grid_for((n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock);
