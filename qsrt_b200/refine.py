@@ -2,7 +2,7 @@
 
 Host mirror of ``qsrt/h2_viterbi_refine.py`` (``refine_h2_viterbi_paths`` :334-560, objectives
 :71-139, ``config_from_quant_args`` :563-590), of the guidance containers of
-``qsrt/gradient_guided_viterbi.py:17-120`` and of ``refine_uniform_h2_candidate``
+``qsrt/gradient_guided_viterbi.py:17-207`` (target shifts included) and of ``refine_uniform_h2_candidate``
 (``qsrt/exl3_encoder_backend.py:840-895``).
 
 After BlockLDLQ every 16-row block is revisited with all quantisation errors known: the exact
@@ -110,6 +110,60 @@ class LowRankViterbiGradientGuidance:
 
 
 GradientGuidance = ViterbiGradientGuidance | LowRankViterbiGradientGuidance
+
+
+def shift_elementwise_target(target: torch.Tensor, gradient: torch.Tensor, *, strength: float,
+                             quadratic_weight: torch.Tensor | float = 1.0) -> torch.Tensor:
+    """Target with the minimiser of ``a (q - target)^2 + strength * gradient * q``
+    (``gradient_guided_viterbi.py:123-152``): the tile search then optimises the guided objective
+    unchanged."""
+
+    if target.shape != gradient.shape:
+        raise ValueError("target and gradient must have matching shapes")
+    if not (target.is_floating_point() and gradient.is_floating_point()):
+        raise TypeError("target and gradient must be floating point")
+    if not math.isfinite(strength) or strength < 0.0:
+        raise ValueError("gradient strength must be finite and nonnegative")
+    weight = torch.as_tensor(quadratic_weight, device=target.device, dtype=torch.float32)
+    if weight.ndim and weight.shape != target.shape:
+        raise ValueError("quadratic weights must be scalar or match the target")
+    if not bool(torch.isfinite(weight).all()) or not bool((weight > 0).all()):
+        raise ValueError("quadratic weights must be finite and positive")
+    return target.float() - 0.5 * float(strength) * gradient.float() / weight
+
+
+def shift_two_sided_target(target: torch.Tensor, gradient: torch.Tensor, row_hessian: torch.Tensor,
+                           column_hessian: torch.Tensor, *, strength: float) -> torch.Tensor:
+    """Completed square under ``tr(E^T H_row E H_column)`` (``gradient_guided_viterbi.py:155-187``):
+    ``target - strength/2 * H_row^-1 G H_column^-1`` by two solves."""
+
+    if target.ndim != 2 or gradient.shape != target.shape:
+        raise ValueError("two-sided target and gradient must be matching matrices")
+    rows, columns = target.shape
+    if tuple(row_hessian.shape) != (rows, rows):
+        raise ValueError("row Hessian has incompatible geometry")
+    if tuple(column_hessian.shape) != (columns, columns):
+        raise ValueError("column Hessian has incompatible geometry")
+    if not math.isfinite(strength) or strength < 0.0:
+        raise ValueError("gradient strength must be finite and nonnegative")
+    dtype = torch.float64 if target.dtype == torch.float64 else torch.float32
+    move = dict(device=target.device, dtype=dtype)
+    left = torch.linalg.solve(row_hessian.to(**move), gradient.to(**move))
+    correction = torch.linalg.solve(column_hessian.to(**move).T, left.T).T
+    if not bool(torch.isfinite(correction).all()):
+        raise FloatingPointError("two-sided gradient target shift is non-finite")
+    return target.to(dtype=dtype) - 0.5 * float(strength) * correction
+
+
+def two_sided_guided_objective(target, candidate, anchor, gradient, row_hessian, column_hessian, *, strength: float):
+    """Quadratic, linear and combined objectives as 0-d tensors (``gradient_guided_viterbi.py:190-207``)."""
+
+    if not (target.shape == candidate.shape == anchor.shape == gradient.shape):
+        raise ValueError("guided objective matrices must have matching shapes")
+    error = candidate - target
+    quadratic = torch.sum(error * (row_hessian @ error @ column_hessian))
+    linear = float(strength) * torch.sum(gradient * (candidate - anchor))
+    return quadratic, linear, quadratic + linear
 
 
 # ---- configuration and results ---------------------------------------------------------------------

@@ -73,3 +73,33 @@ def test_refinement_refuses_cpu_tensors():
     weight = torch.zeros((16, 16))
     with pytest.raises(ValueError, match="requires CUDA"):
         refine.refine_h2_viterbi_paths(weight, torch.eye(16), weight, torch.zeros((1, 1, 256), dtype=torch.int16), {})
+
+
+def test_target_shifts_complete_the_square():
+    g = torch.Generator().manual_seed(3)
+    target, gradient = torch.randn((8, 12), generator=g), torch.randn((8, 12), generator=g)
+    weight = torch.rand((8, 12), generator=g) + 0.5
+    shifted = refine.shift_elementwise_target(target, gradient, strength=0.8, quadratic_weight=weight)
+    # stationarity of a (q - t)^2 + s g q at q = shifted
+    assert torch.allclose(2 * weight * (shifted - target) + 0.8 * gradient, torch.zeros_like(target), atol=1e-6)
+    assert torch.equal(refine.shift_elementwise_target(target, gradient, strength=0.0), target)
+    with pytest.raises(ValueError, match="matching shapes"):
+        refine.shift_elementwise_target(target, gradient[:-1], strength=1.0)
+    with pytest.raises(ValueError, match="finite and positive"):
+        refine.shift_elementwise_target(target, gradient, strength=1.0, quadratic_weight=0.0)
+    with pytest.raises(TypeError):
+        refine.shift_elementwise_target(target.long(), gradient, strength=1.0)
+
+    row, column = helpers.spd_hessian(8, 4.0, 5).double(), helpers.spd_hessian(12, 6.0, 6).double()
+    t64, g64 = target.double(), gradient.double()
+    two = refine.shift_two_sided_target(t64, g64, row, column, strength=0.6)
+    # gradient of tr(E^T R E C) + s <G, Q> vanishes at Q = two
+    residual = 2 * row @ (two - t64) @ column + 0.6 * g64
+    assert float(residual.abs().max()) < 1e-10
+    anchor = torch.zeros_like(t64)
+    quadratic, linear, total = refine.two_sided_guided_objective(t64, two, anchor, g64, row, column, strength=0.6)
+    assert float(total) == float(quadratic + linear)
+    bumped = two + 1e-3 * torch.randn(two.shape, generator=g, dtype=torch.float64)
+    assert float(refine.two_sided_guided_objective(t64, bumped, anchor, g64, row, column, strength=0.6)[2]) > float(total)
+    with pytest.raises(ValueError, match="row Hessian"):
+        refine.shift_two_sided_target(t64, g64, column, column, strength=0.6)
