@@ -1243,3 +1243,6 @@ from .candidates import (  # noqa: E402
     ldlq_mixed_k_candidates_prefix_reuse,
     ldlq_mixed_n_candidates_reuse,
 )
+
+# dense-H path refinement, part of the reference module's surface (exl3_encoder_backend.py:20-23, 840)
+from .refine import refine_h2_viterbi_paths, refine_uniform_h2_candidate  # noqa: E402
