@@ -237,3 +237,33 @@ def matrix_to_tc_tiles(matrix: torch.Tensor, order: torch.Tensor) -> torch.Tenso
 
 def tc_tiles_to_matrix(tiles: torch.Tensor, inverse: torch.Tensor, rows: int, columns: int) -> torch.Tensor:
     return tiles[:, inverse].reshape(rows // 16, columns // 16, 16, 16).permute(0, 2, 1, 3).reshape(rows, columns)
+
+
+# ---- quantize_qsrt cases pinned by the reference's own encoder code ---------------------------------
+ENCODER_CASES = {
+    # name: (bits, in, out, g_scale_override, apply_out_scales, sigma_reg)
+    "k3_override": (3, 256, 128, 0.9, False, 1e-2),
+    "k2_override_auto_scales": (2, 256, 128, 1.15, None, 0.025),
+    "k4_override_out_scales": (4, 128, 256, 0.8, True, 0.025),
+    "k2_scale_search": (2, 128, 128, None, False, 1e-2),
+}
+
+
+def encoder_case_inputs(name: str):
+    """Seeded weight [in, out] and capture Hessian of one encoder case (CPU float32)."""
+
+    bits, k, n, _, _, _ = ENCODER_CASES[name]
+    g = torch.Generator().manual_seed(4000 + 13 * bits + k + n)
+    x = torch.randn((4 * k, k), generator=g) * torch.exp(0.5 * torch.randn(k, generator=g))
+    hessian = (x.T @ x / x.shape[0]).float()
+    weight = 0.02 * torch.randn((k, n), generator=g) * torch.exp(0.3 * torch.randn(n, generator=g))
+    return weight, hessian
+
+
+def encoder_case_args(name: str, device: str, table: torch.Tensor) -> dict:
+    bits, _, _, override, out_scales, sigma = ENCODER_CASES[name]
+    args = {"K": bits, "seed": 11, "sv_seed": 12, "sigma_reg": sigma, "devices": [device], "device_ratios": None,
+            "apply_out_scales": out_scales, "ldlq_tf32": False, "tailbite_context": 128, "sqg_e4m3_lut": table}
+    if override is not None:
+        args["g_scale_override"] = override
+    return args
