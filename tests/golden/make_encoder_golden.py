@@ -4,7 +4,8 @@
 
 qsrt/exl3_encoder_backend.py is written to live inside an ExLlamaV3 checkout (relative imports of
 its extension and utilities) and to run on CUDA tensors.  This script loads the unmodified file
-under a stand-in package and supplies only what lies outside the file:
+under a stand-in package (one device-placement guard of ldlq_mixed_batched lifted, see
+load_reference_encoder) and supplies only what lies outside the file:
 
   * ext.pack_trellis            -> the pinned packer restatement (oracle.qsrt_oracle);
   * quantize_tiles              -> the C restatement of the reference's tile search, bit-exact
@@ -20,7 +21,9 @@ under a stand-in package and supplies only what lies outside the file:
 Everything else - Hessian preparation and congruence, block LDL, regularisation, scale search,
 the BlockLDLQ recursion, proxy error, packing - is the reference's code.  Stored per case: the
 initial sign vectors, suh, svh, the packed trellis, g_scale, proxy error and probes of L and the
-work-coordinate Hessian.
+work-coordinate Hessian.  Candidate grids go through the reference's quantize_qsrt_batch (mixed-rate
+LDLQ with the output-axis reuse and the input-axis prefix trie); stored per candidate: a 64-bit
+digest of every tile's states, proxy error, suh, svh.
 """
 
 import contextlib
@@ -36,7 +39,10 @@ import torch
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 from oracle import qsrt_oracle  # noqa: E402
-from tests.helpers import ENCODER_CASES, encoder_case_args, encoder_case_inputs  # noqa: E402
+from tests.helpers import (  # noqa: E402
+    BATCH_CASES, ENCODER_CASES, batch_case_args, batch_case_inputs, encoder_case_args, encoder_case_inputs,
+    tile_digests,
+)
 
 
 def _module(name: str, **attrs):
@@ -107,7 +113,14 @@ def load_reference_encoder():
     torch.cuda.stream = lambda stream: contextlib.nullcontext()
     to_host = torch.Tensor.cpu
     torch.Tensor.cpu = lambda self, *a, **k: self.clone() if self.device.type == "cpu" else to_host(self, *a, **k)
-    spec.loader.exec_module(module)
+    # ldlq_mixed_batched refuses tensors that are not on a CUDA device; that one placement guard is
+    # lifted so that the candidate-grid code can run here.  Nothing else of the file is touched.
+    text = source.read_text()
+    guard = 'if weights.device != Ls.device or weights.device.type != "cuda":'
+    assert text.count(guard) == 1
+    text = text.replace(guard, "if weights.device != Ls.device:")
+    module.__file__ = str(source)
+    exec(compile(text, str(source), "exec"), module.__dict__)
     module.quantize_tiles = _quantize_tiles
     return module
 
@@ -139,6 +152,25 @@ def main() -> None:
         out[f"{name}_H_probe"] = (h_data["H"] @ vector).numpy()
         out[f"{name}_weight_q_probe"] = (vector @ weight_q).numpy()
         print(name, "g_scale", args["g_scale"], "proxy", proxy, "apply_out_scales", args["apply_out_scales"])
+    # candidate grids through the reference's quantize_qsrt_batch (reuse schedules included)
+    tables_by_bits = {bits: sqg_xor_cheb_t12_bytes(bits) for bits in (2, 3, 4)}
+    for name in BATCH_CASES:
+        sources = batch_case_inputs(name)
+        groups = [batch_case_args(name, "cpu", tables_by_bits) for _ in sources]
+        h_datas = [make_shared_h(w.shape[0], torch.device("cpu"), h) for w, h in sources]
+        results = encoder.quantize_qsrt_batch([w.clone() for w, _ in sources], h_datas, groups, return_weight_q=False)
+        # su = sign * rms / (-c): the drawn sign is the opposite of the stored vector's
+        out[f"{name}_su_sign"] = torch.sign(-results[0][0]["suh"].float()).to(torch.int8).numpy()
+        out[f"{name}_sv_sign"] = torch.sign(encoder.output_signs(sources[0][0].shape[1], torch.device("cpu"),
+                                                                 groups[0][0])).flatten().to(torch.int8).numpy()
+        for s_index, group in enumerate(results):
+            for c_index, result in enumerate(group):
+                key = f"{name}_{s_index}_{c_index}"
+                out[f"{key}_tiles"] = tile_digests(result["encoded"].numpy())
+                out[f"{key}_proxy"] = np.float64(result["proxy"])
+                out[f"{key}_suh"] = result["suh"].numpy()
+                out[f"{key}_svh"] = result["svh"].numpy()
+                print(key, "proxy", result["proxy"], "g_scale", result["g_scale"])
     path = ROOT / "tests" / "golden" / "encoder_golden.npz"
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -267,3 +267,42 @@ def encoder_case_args(name: str, device: str, table: torch.Tensor) -> dict:
     if override is not None:
         args["g_scale_override"] = override
     return args
+
+
+# ---- quantize_qsrt_batch cases (candidate grids) pinned the same way -------------------------------
+BATCH_SHAPE = (256, 256)
+BATCH_CASES = {
+    # name: (rate axis, rate maps per source; the first map is the all-K3 base)
+    "n_axis_reuse": ("n", ([3] * 16, [2] * 4 + [3] * 8 + [4] * 4, [2] * 8 + [4] * 8)),
+    "k_axis_prefix": ("k", ([3] * 16, [2] * 4 + [4] * 4 + [3] * 8, [3] * 4 + [4] * 4 + [3] * 8)),
+}
+
+
+def batch_case_inputs(name: str, sources: int = 2):
+    """Seeded weights [in, out] and capture Hessians of one candidate-grid case (CPU float32)."""
+
+    k, n = BATCH_SHAPE
+    out = []
+    for index in range(sources):
+        g = torch.Generator().manual_seed(7000 + 31 * index + (name == "k_axis_prefix"))
+        x = torch.randn((4 * k, k), generator=g) * torch.exp(0.5 * torch.randn(k, generator=g))
+        out.append((0.02 * torch.randn((k, n), generator=g), (x.T @ x / x.shape[0]).float()))
+    return out
+
+
+def batch_case_args(name: str, device: str, tables_by_bits: dict) -> list[dict]:
+    axis, maps = BATCH_CASES[name]
+    return [{"K": 3, "seed": 11, "sv_seed": 12, "sigma_reg": 0.025, "devices": [device], "device_ratios": None,
+             "apply_out_scales": False, "ldlq_tf32": False, "tailbite_context": 128, "buf_size_k": 128,
+             "g_scale_override": 0.95, "sqg_e4m3_luts_by_bits": tables_by_bits, "mixed_rate_axis": axis,
+             "mixed_tile_bits": tuple(m)} for m in maps]
+
+
+def tile_digests(states) -> np.ndarray:
+    """64-bit digest of every tile's 256 states ([..., 256] int16 -> [...] uint64)."""
+
+    import hashlib
+
+    flat = np.ascontiguousarray(np.asarray(states).reshape(-1, 256).astype(np.int16))
+    return np.array([int.from_bytes(hashlib.blake2b(row.tobytes(), digest_size=8).digest(), "little") for row in flat],
+                    dtype=np.uint64)

@@ -14,6 +14,7 @@ import torch
 
 from oracle import qsrt_oracle as oracle
 from qsrt_b200 import encoder, tables
+from tests import helpers
 
 pytestmark = pytest.mark.gpu
 
@@ -246,3 +247,40 @@ def test_rate_transfer_candidates_at_native_geometry_pack_into_records_and_atoms
                 else:
                     assert torch.equal(states[:, 4 * 8:], previous[:, 4 * 8:])
             previous = states
+
+
+@pytest.mark.parametrize("name", list(helpers.BATCH_CASES))
+def test_quantize_qsrt_batch_against_reference_run(cuda_device, monkeypatch, name):
+    """Candidate grids through quantize_qsrt_batch against what the reference's own
+    quantize_qsrt_batch produced for the same seeded sources (tests/golden/encoder_golden.npz; the
+    reference code run on the CPU around the pinned tile search, with its output-axis reuse and
+    input-axis prefix schedules).  Sign vectors are injected (device-generator draws in the
+    reference).  Bars: scale vectors equal up to fp16 rounding of float32 sums, tile identity
+    >= 85 % per candidate (free-running recursion), proxy error within 2 %."""
+
+    from pathlib import Path
+
+    golden = np.load(Path(__file__).parent / "golden" / "encoder_golden.npz")
+    signs = {11: golden[f"{name}_su_sign"], 12: golden[f"{name}_sv_sign"]}
+    monkeypatch.setattr(encoder, "_signs", lambda length, device, seed: torch.from_numpy(
+        signs[seed].astype(np.float32)).to(device))
+    sources = helpers.batch_case_inputs(name)
+    groups = [helpers.batch_case_args(name, str(cuda_device), LUTS) for _ in sources]
+    h_datas = [encoder.make_shared_h(w.shape[0], cuda_device, h) for w, h in sources]
+    results = encoder.quantize_qsrt_batch([w.clone().to(cuda_device) for w, _ in sources], h_datas, groups,
+                                          return_weight_q=False)
+    assert len(results) == len(sources) and all(len(group) == len(groups[0]) for group in results)
+    identities = []
+    for s_index, group in enumerate(results):
+        for c_index, result in enumerate(group):
+            key = f"{name}_{s_index}_{c_index}"
+            for part in ("suh", "svh"):
+                got = result[part].cpu().numpy().view(np.int16).astype(np.int32)
+                want = golden[f"{key}_{part}"].view(np.int16).astype(np.int32)
+                assert np.abs(got - want).max() <= 1 and (got == want).mean() >= 0.97, (key, part)
+            same = helpers.tile_digests(result["encoded"].cpu().numpy()) == golden[f"{key}_tiles"]
+            identities.append(float(same.mean()))
+            assert same.mean() >= 0.85, f"{key}: tile identity {same.mean():.4f}"
+            want = float(golden[f"{key}_proxy"])
+            assert abs(result["proxy"] - want) <= 2e-2 * want, key
+    print(name, "tile identity per candidate:", identities)
