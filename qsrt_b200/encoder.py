@@ -807,7 +807,8 @@ def fallback_quant(weight: torch.Tensor, device, quant_args: dict, pb=None):
             batch=1, n=size_n, ld=size_n, w_stride=0, comp_ld=size_n, comp_stride=0, state_stride=0,
         )
     del zero
-    mse = (weight - weight_q).square().mean().item() / max(weight.square().mean().item(), 1e-20)
+    # mean squared error of the regularised weight, summed in float64 (:1923-1946)
+    mse = (torch.sum((weight.float() - weight_q.float()).pow(2), dtype=torch.float64) / weight.numel()).item()
     return weight_q, encoded, mse
 
 

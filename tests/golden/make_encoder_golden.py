@@ -40,7 +40,7 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 from oracle import qsrt_oracle  # noqa: E402
 from tests.helpers import (  # noqa: E402
-    BATCH_CASES, ENCODER_CASES, batch_case_args, batch_case_inputs, encoder_case_args, encoder_case_inputs,
+    BATCH_CASES, ENCODER_CAPTURE_COUNT, ENCODER_CASES, batch_case_args, batch_case_inputs, encoder_case_args, encoder_case_inputs,
     tile_digests,
 )
 
@@ -126,16 +126,23 @@ def load_reference_encoder():
 
 
 def main() -> None:
+    """With case names as arguments only those cases are run and merged into the stored file."""
+
     from qsrt.ldlq import make_shared_h
     from qsrt.sqg_e4m3 import sqg_xor_cheb_t12_bytes
 
     encoder = load_reference_encoder()
-    probe = torch.Generator().manual_seed(99)
-    out = {}
+    path = ROOT / "tests" / "golden" / "encoder_golden.npz"
+    only = set(sys.argv[1:])
+    out = dict(np.load(path)) if only else {}
     for name, (bits, k, n, _, _, _) in ENCODER_CASES.items():
+        if only and name not in only:
+            continue
+        probe = torch.Generator().manual_seed(99 + k + n + bits)
         weight, hessian = encoder_case_inputs(name)
         args = encoder_case_args(name, "cpu", sqg_xor_cheb_t12_bytes(bits))
         h_data = make_shared_h(k, torch.device("cpu"), hessian)
+        h_data["count"] = ENCODER_CAPTURE_COUNT.get(name, h_data["count"])
         weight_q, proxy, tensors = encoder.quantize_qsrt(weight.clone(), h_data, args, True)
         vector = torch.randn(k, generator=probe)
         out[f"{name}_su_sign"] = torch.sign(-tensors["suh"].float()).to(torch.int8).numpy()  # su = sign * rms / (-c)
@@ -148,13 +155,21 @@ def main() -> None:
         out[f"{name}_proxy"] = np.float64(proxy)
         out[f"{name}_apply_out_scales"] = np.bool_(args["apply_out_scales"])
         out[f"{name}_probe"] = vector.numpy()
-        out[f"{name}_L_probe"] = (h_data["L"] @ vector).numpy()
-        out[f"{name}_H_probe"] = (h_data["H"] @ vector).numpy()
+        if h_data["L"] is not None:
+            out[f"{name}_L_probe"] = (h_data["L"] @ vector).numpy()
+            out[f"{name}_H_probe"] = (h_data["H"] @ vector).numpy()
+        receipt = args.get("h2_viterbi_refine_receipt") or {}
+        if receipt.get("enabled"):
+            out[f"{name}_refine_accepted"] = np.int64(receipt["sweeps"][0]["accepted_tiles"])
+            out[f"{name}_refine_objective"] = np.float64([receipt["sweeps"][0]["objective_before"],
+                                                          receipt["sweeps"][0]["objective_after"]])
         out[f"{name}_weight_q_probe"] = (vector @ weight_q).numpy()
         print(name, "g_scale", args["g_scale"], "proxy", proxy, "apply_out_scales", args["apply_out_scales"])
     # candidate grids through the reference's quantize_qsrt_batch (reuse schedules included)
     tables_by_bits = {bits: sqg_xor_cheb_t12_bytes(bits) for bits in (2, 3, 4)}
     for name in BATCH_CASES:
+        if only and name not in only:
+            continue
         sources = batch_case_inputs(name)
         groups = [batch_case_args(name, "cpu", tables_by_bits) for _ in sources]
         h_datas = [make_shared_h(w.shape[0], torch.device("cpu"), h) for w, h in sources]
@@ -171,7 +186,6 @@ def main() -> None:
                 out[f"{key}_suh"] = result["suh"].numpy()
                 out[f"{key}_svh"] = result["svh"].numpy()
                 print(key, "proxy", result["proxy"], "g_scale", result["g_scale"])
-    path = ROOT / "tests" / "golden" / "encoder_golden.npz"
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")
 

@@ -246,7 +246,12 @@ ENCODER_CASES = {
     "k2_override_auto_scales": (2, 256, 128, 1.15, None, 0.025),
     "k4_override_out_scales": (4, 128, 256, 0.8, True, 0.025),
     "k2_scale_search": (2, 128, 128, None, False, 1e-2),
+    "k3_no_hessian_fallback": (3, 128, 128, 0.9, True, 1e-2),
+    "k3_refine_sweep": (3, 128, 128, 0.9, False, 1e-2),
 }
+# extra quant_args and the sample count of the capture (0 = no Hessian: the fallback path)
+ENCODER_EXTRA_ARGS = {"k3_refine_sweep": {"h2_viterbi_refine_sweeps": 1}}
+ENCODER_CAPTURE_COUNT = {"k3_no_hessian_fallback": 0}
 
 
 def encoder_case_inputs(name: str):
@@ -266,6 +271,7 @@ def encoder_case_args(name: str, device: str, table: torch.Tensor) -> dict:
             "apply_out_scales": out_scales, "ldlq_tf32": False, "tailbite_context": 128, "sqg_e4m3_lut": table}
     if override is not None:
         args["g_scale_override"] = override
+    args.update(ENCODER_EXTRA_ARGS.get(name, {}))
     return args
 
 
