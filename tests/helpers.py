@@ -248,6 +248,7 @@ ENCODER_CASES = {
     "k2_scale_search": (2, 128, 128, None, False, 1e-2),
     "k3_no_hessian_fallback": (3, 128, 128, 0.9, True, 1e-2),
     "k3_refine_sweep": (3, 128, 128, 0.9, False, 1e-2),
+    "k3_1024_tiles_scale_search": (3, 512, 512, None, None, 0.025),
 }
 # extra quant_args and the sample count of the capture (0 = no Hessian: the fallback path)
 ENCODER_EXTRA_ARGS = {"k3_refine_sweep": {"h2_viterbi_refine_sweeps": 1}}

@@ -385,7 +385,8 @@ def test_quantize_qsrt_against_reference_run(cuda_device, monkeypatch, name):
         assert h_data["L"] is None
     want_proxy = float(golden[f"{name}_proxy"])
     assert abs(proxy - want_proxy) <= (2e-2 if override is None else 1e-2) * want_proxy
-    if override is not None:
+    if override is not None or abs(args["g_scale"] - want_g) <= 1e-6 * want_g:
+        # (a searched scale that agrees to 1e-6 leaves the same encoder input up to float32 rounding)
         got_states = codec.unpack_trellis_states(tensors["trellis"], bits).cpu().numpy().reshape(-1, 256)
         want_states = oracle.unpack_trellis_states(golden[f"{name}_trellis"].reshape(-1, 16 * bits), bits)
         same = (got_states == want_states).all(axis=-1)
