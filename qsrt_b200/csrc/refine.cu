@@ -23,7 +23,7 @@ __device__ __forceinline__ T block_sum(T value, T* partial)
 {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) value += __shfl_xor_sync(0xffffffffu, value, o);
-    __syncthreads();  // the previous round's readers are done with `partial`
+    __syncthreads();  // the previous reduction's readers are done with `partial`
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = value;
     __syncthreads();
     T total = partial[0];
