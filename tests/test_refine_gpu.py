@@ -211,3 +211,37 @@ def test_quantize_qsrt_with_refinement_sweeps(cuda_device):
                                         tensors["svh"].cpu().numpy(), lut)
     rel = np.linalg.norm(weight_q.cpu().numpy() - decoded) / np.linalg.norm(decoded)
     assert rel < 2e-3
+
+
+def test_full_size_down_projection_sweep_properties(cuda_device):
+    """One sweep over a down projection of the headline shape ([2048, 7168] in encoder orientation,
+    57 344 tiles, K3), checked through size-independent properties: the objective the sweep reports
+    equals the directly evaluated one and does not rise, every accepted path is a closed legal path,
+    and the stored reconstruction is the decode of the stored payload."""
+
+    rows, columns = 2048, 7168
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    weight = 1.2 * torch.randn((rows, columns), device=cuda_device, generator=g)
+    x = torch.randn((4 * rows, rows), device=cuda_device, generator=g)
+    x *= torch.exp(0.5 * torch.randn(rows, device=cuda_device, generator=g))
+    hessian = x.T @ x / x.shape[0]
+    hessian.diagonal().add_(0.025 * hessian.diagonal().mean())
+    args = _quant_args(3, cuda_device)
+    initial_q, initial_states = _initial(weight, args, cuda_device)
+    before = refine.dense_h_objective(weight, initial_q, hessian, dtype=torch.float32)
+    result = refine.refine_h2_viterbi_paths(weight, hessian, initial_q, initial_states, args,
+                                            refine.H2ViterbiRefineConfig(sweeps=1))
+    stats = result.sweep_stats[0]
+    assert stats.proposed_tiles == (rows // 16) * (columns // 16)
+    assert stats.accepted_tiles > 0 and stats.objective_after < stats.objective_before
+    assert abs(stats.objective_before - before) <= 1e-3 * before
+    after = refine.dense_h_objective(weight, result.weight_q, hessian, dtype=torch.float32)
+    assert abs(stats.objective_after - after) <= 1e-3 * after
+    changed = (result.encoded != initial_states).any(dim=-1)
+    assert int(changed.sum()) == stats.accepted_tiles
+    assert stats.proposed_tiles <= stats.unique_candidate_paths <= 2 * stats.proposed_tiles
+    assert qsrt_oracle.states_close(result.encoded[changed].cpu().numpy().reshape(-1, 256), 3)
+    lut = torch.from_numpy(qsrt_oracle.e4m3_to_float(args["sqg_e4m3_lut"].numpy())).to(cuda_device)
+    order = encoder.tensor_core_perm(cuda_device)
+    decoded = lut[result.encoded.reshape(-1, 256).long() & 0xFFFF]
+    assert torch.equal(helpers.tc_tiles_to_matrix(decoded, torch.argsort(order), rows, columns), result.weight_q)
