@@ -245,3 +245,38 @@ def test_full_size_down_projection_sweep_properties(cuda_device):
     order = encoder.tensor_core_perm(cuda_device)
     decoded = lut[result.encoded.reshape(-1, 256).long() & 0xFFFF]
     assert torch.equal(helpers.tc_tiles_to_matrix(decoded, torch.argsort(order), rows, columns), result.weight_q)
+
+
+def test_quantize_qsrt_batch_refines_uniform_candidates(cuda_device):
+    """quantize_qsrt_batch revisits every finished candidate (exl3_encoder_backend.py:3296-3312):
+    uniform rate maps are refined, a receipt is returned per candidate, and a map with more than
+    one rate is refused as in the reference."""
+
+    sources = helpers.batch_case_inputs("n_axis_reuse", sources=1)
+    luts = {b: tables.sqg_xor_cheb_t12_bytes(b) for b in (2, 3, 4)}
+
+    def groups(maps, **extra):
+        out = []
+        for m in maps:
+            args = helpers.batch_case_args("n_axis_reuse", str(cuda_device), luts)[0]
+            args.update(mixed_tile_bits=tuple(m), **extra)
+            out.append(args)
+        return [out]
+
+    def run(group):
+        h_datas = [encoder.make_shared_h(w.shape[0], cuda_device, h) for w, h in sources]
+        return encoder.quantize_qsrt_batch([w.clone().to(cuda_device) for w, _ in sources], h_datas, group,
+                                           return_weight_q=False)[0]
+
+    plain = run(groups([[3] * 16, [4] * 16]))
+    refined = run(groups([[3] * 16, [4] * 16], h2_viterbi_refine_sweeps=1))
+    for before, after, bits in zip(plain, refined, (3, 4)):
+        assert before["h2_viterbi_refine"] == {"enabled": False, "sweeps": []}
+        receipt = after["h2_viterbi_refine"]
+        assert receipt["enabled"] and receipt["rate_bits"] == bits and len(receipt["sweeps"]) == 1
+        assert after["proxy"] <= before["proxy"] * (1 + 1e-6)
+        if receipt["sweeps"][0]["accepted_tiles"]:
+            assert after["proxy"] < before["proxy"]
+        assert qsrt_oracle.states_close(after["encoded"].cpu().numpy().reshape(-1, 256), bits)
+    with pytest.raises(ValueError, match="uniform rate map"):
+        run(groups([[3] * 16, [2] * 8 + [4] * 8], h2_viterbi_refine_sweeps=1))
