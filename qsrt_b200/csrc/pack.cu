@@ -168,7 +168,9 @@ decode_e4m3_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int bit
 // One warp per tile.  Lane l holds tensor-core elements 8l..8l+7, i.e. rows {r0, r0+1, r0+8,
 // r0+9} x columns {c0, c0+8} with r0 = 2*(l%4), c0 = l/4 (exl3_encoder_backend.py:35-57): each
 // of its 8 stores lands in a run of 8 consecutive floats shared with 7 other lanes.
-__global__ void __launch_bounds__(32 * kWarpsPerBlock)
+// One 1024-thread CTA per SM stages the table once; a warp takes two tiles per iteration so that
+// both 512-byte loads are in flight before the first look-up.
+__global__ void __launch_bounds__(1024, 1)
 states_to_matrix_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, int tiles_n,
                         const uint8_t* __restrict__ lut_state, float* __restrict__ out, int ld)
 {
@@ -180,24 +182,37 @@ states_to_matrix_kernel(const uint16_t* __restrict__ states, int64_t n_tiles, in
     }
     const int lane = threadIdx.x & 31;
     const int r0 = (lane & 3) * 2, c0 = lane >> 2;
-    for (int64_t tile = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); tile < n_tiles;
-         tile += int64_t(gridDim.x) * kWarpsPerBlock) {
-        const uint4 v = reinterpret_cast<const uint4*>(states + tile * 256)[lane];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        const int64_t tk = tile / tiles_n;
-        const int tn = int(tile - tk * tiles_n);
-        float* base = out + (tk * 16) * int64_t(ld) + tn * 16;
+    const int64_t warps = int64_t(gridDim.x) * 32;
+    const int64_t pairs = (n_tiles + 1) / 2;
+    for (int64_t pair = int64_t(blockIdx.x) * 32 + (threadIdx.x >> 5); pair < pairs; pair += warps) {
+        uint4 v[2];
+        bool live[2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t state = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
-            const uint8_t b = sh_lut[state];
-            // E4M3 -> float: exact, via the bit pattern
-            const int ex = (b >> 3) & 15, m = b & 7;
-            float value = ex == 0 ? float(m) * 0.001953125f : __int_as_float(((ex + 120) << 23) | (m << 20));
-            if (b & 0x80) value = -value;
-            const int row = r0 + (j & 1) + ((j & 2) ? 8 : 0);
-            const int col = c0 + ((j & 4) ? 8 : 0);
-            base[int64_t(row) * ld + col] = value;
+        for (int u = 0; u < 2; ++u) {
+            const int64_t tile = 2 * pair + u;
+            live[u] = tile < n_tiles;
+            v[u] = reinterpret_cast<const uint4*>(states + (live[u] ? tile : 0) * 256)[lane];
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!live[u]) continue;
+            const int64_t tile = 2 * pair + u;
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            const int64_t tk = tile / tiles_n;
+            const int tn = int(tile - tk * tiles_n);
+            float* base = out + (tk * 16) * int64_t(ld) + tn * 16;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t state = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+                const uint8_t b = sh_lut[state];
+                // E4M3 -> float: exact, via the bit pattern
+                const int ex = (b >> 3) & 15, m = b & 7;
+                float value = ex == 0 ? float(m) * 0.001953125f : __int_as_float(((ex + 120) << 23) | (m << 20));
+                if (b & 0x80) value = -value;
+                const int row = r0 + (j & 1) + ((j & 2) ? 8 : 0);
+                const int col = c0 + ((j & 4) ? 8 : 0);
+                base[int64_t(row) * ld + col] = value;
+            }
         }
     }
 }
@@ -279,7 +294,11 @@ extern "C" int qsrtb_states_to_matrix(const int16_t* states, int tiles_k, int ti
     if (n_tiles == 0) return QSRTB_OK;
     if (!states || !lut_state || !out) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
     cudaFuncSetAttribute(states_to_matrix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-    states_to_matrix_kernel<<<lut_grid(n_tiles), 32 * kWarpsPerBlock, 65536, static_cast<cudaStream_t>(stream)>>>(
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int64_t wanted = (n_tiles + 63) / 64;   // 32 warps x 2 tiles per block and iteration
+    states_to_matrix_kernel<<<int(wanted < sms ? wanted : sms), 1024, 65536, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(states), n_tiles, tiles_n, lut_state, out, ld);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "states_to_matrix launch");
