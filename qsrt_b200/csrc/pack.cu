@@ -115,6 +115,46 @@ unpack_decode_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int b
     }
 }
 
+// States only (no table): two tiles per warp and iteration, both loads issued before the first
+// shuffle, so that a warp keeps two independent 512-byte stores behind one load latency.
+__global__ void __launch_bounds__(32 * kWarpsPerBlock)
+unpack_states_kernel(const uint32_t* __restrict__ packed, int64_t n_tiles, int bits, uint16_t* __restrict__ out_states)
+{
+    const int lane = threadIdx.x & 31;
+    const int chunk_bits = 8 * bits, words_per_tile = 8 * bits;
+    const unsigned long long chunk_mask = (1ull << chunk_bits) - 1ull;
+    const int bit0 = lane * chunk_bits;
+    const int w = bit0 >> 5, off = bit0 & 31;
+    const int w_next = min(w + 1, words_per_tile - 1);
+    const int64_t warps = int64_t(gridDim.x) * kWarpsPerBlock;
+    const int64_t pairs = (n_tiles + 1) / 2;
+    for (int64_t pair = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); pair < pairs; pair += warps) {
+        uint32_t w0[2], w1[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int64_t tile = 2 * pair + u;
+            live[u] = tile < n_tiles;
+            const uint32_t* words = packed + (live[u] ? tile : 0) * words_per_tile;
+            w0[u] = words[w];
+            w1[u] = words[w_next];
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned long long two = (static_cast<unsigned long long>(w0[u]) << 32) | w1[u];
+            const uint32_t chunk = uint32_t((two >> (64 - off - chunk_bits)) & chunk_mask);
+            const uint32_t prev = __shfl_sync(0xffffffffu, chunk, (lane + 31) & 31);
+            const unsigned long long window = (static_cast<unsigned long long>(prev) << chunk_bits) | chunk;
+            uint32_t st[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st[i] = uint32_t(window >> ((7 - i) * bits)) & 0xffffu;
+            if (live[u])
+                reinterpret_cast<uint4*>(out_states + (2 * pair + u) * 256)[lane] =
+                    make_uint4(st[0] | (st[1] << 16), st[2] | (st[3] << 16), st[4] | (st[5] << 16), st[6] | (st[7] << 16));
+        }
+    }
+}
+
 // Labels only: 32 warps per SM share one staged copy of the table (one 1024-thread CTA per SM) and
 // every warp decodes two tiles per iteration, so two tiles' loads and their 16 table look-ups per
 // lane are in flight together; with one tile per warp the kernel waited on its own load latency.
@@ -273,6 +313,14 @@ extern "C" int qsrtb_unpack_decode(const int16_t* packed, int64_t n_tiles, int b
             reinterpret_cast<const uint32_t*>(packed), n_tiles, bits, lut_state, out_e4m3);
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return qsrtb_fail_cuda(e, "decode launch");
+        return QSRTB_OK;
+    }
+    if (out_states && !out_e4m3) {
+        unpack_states_kernel<<<grid_for((n_tiles + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock)), 32 * kWarpsPerBlock, 0,
+                               static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const uint32_t*>(packed), n_tiles, bits, reinterpret_cast<uint16_t*>(out_states));
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return qsrtb_fail_cuda(e, "unpack launch");
         return QSRTB_OK;
     }
     const size_t smem = out_e4m3 ? 65536 : 0;
