@@ -58,10 +58,12 @@ int qsrtb_lut_prepare(const uint8_t* lut_state, int bits, uint8_t* lut_pm, float
  */
 int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 
-/* Tuning knob without a reference counterpart: work units per thread of the search kernel
- * (2 = 512 threads holding half2 labels in registers, 1 = 1024 threads holding fp8 labels,
- * 0 = per-rate default).  Process-wide; results are identical. */
-int qsrtb_viterbi_set_units(int units);
+/* `variant` of the search entry points: bit 0 = dedicated K2 arithmetic (bits == 2 only);
+ * bits 4-5 = thread layout of the search kernel, a per-call tuning choice without a reference
+ * counterpart (0 = per-rate default, 1 = 1024 threads holding fp8 labels, 2 = 512 threads
+ * holding half2 labels in registers).  Results are identical for every layout. */
+#define QSRTB_VARIANT_DEDICATED_K2 1
+#define QSRTB_VARIANT_LAYOUT(units) ((units) << 4)
 
 int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-core order   */
                          int64_t n_tiles,
@@ -69,7 +71,7 @@ int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-cor
                          const uint8_t* lut_pm,      /* from qsrtb_lut_prepare             */
                          int bits,                   /* 2, 3 or 4                          */
                          int tailbite_context,       /* 1..128                             */
-                         int variant,                /* 0 generic, 1 dedicated K2          */
+                         int variant,                /* see QSRTB_VARIANT_* above           */
                          float* out_tiles,           /* [n_tiles, 256] reconstruction      */
                          int16_t* out_states,        /* [n_tiles, 256] 16-bit states       */
                          void* scratch, size_t scratch_bytes,
@@ -81,8 +83,10 @@ int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-cor
  * the library image on each GPU, so the call performs no allocation of any kind.
  *   - at most 4096 tiles per call (QSRTB_EINVAL beyond that); the small scratch limits the
  *     grid to 16 CTAs (K2, K3) or 32 (K4), so it is slower than the regular entry point;
- *   - the first call on a device looks up the array's device address; make that first call
- *     outside any stream capture;
+ *   - the first call on a device looks up the array's device address, and is also the moment
+ *     the CUDA runtime may make the library's code and this array resident on that GPU; make
+ *     that first call at start-up - outside any stream capture and before a memory pool claims
+ *     whatever device memory is left;
  *   - all calls share the array: calls that overlap in time on one GPU race, serialise them.
  */
 int qsrtb_quantize_tiles_static(const float* tiles, int64_t n_tiles, const uint8_t* lut_state,
@@ -146,6 +150,56 @@ int qsrtb_signed_block_hadamard(float* x, int64_t rows, int cols, int ld, int ax
 int qsrtb_col_sumsq(const float* x, int batch, int rows, int cols, int ld, int64_t x_stride,
                     float* out, int64_t out_stride, float* workspace, size_t workspace_bytes,
                     void* stream);
+
+/* ---- float32-accurate products on the tensor cores -------------------------------------------
+ * qsrtb_gemm3x_tc:  D[z] = alpha * A[z] * B[z]^T + beta * D[z]  for z < batch, with A [m, k] and
+ * B [n, k] both stored with k contiguous ("K-major").  Stands in for the library float32 GEMMs of
+ * the path: the BlockLDLQ feedback `addmm_` / `baddbmm` (qsrt/exl3_encoder_backend.py:494-501,
+ * 533-534, 1170-1187), the trailing update inside `torch.linalg.cholesky` (:335) and the
+ * `F.linear` products of the routed scoring (qsrt/pooled_calibration.py:734-753).
+ * tcgen05 TF32 MMAs with the accumulator in tensor memory; each operand is passed as two planes,
+ * the TF32 head and tail of the float32 values (qsrtb_split_tf32), and three products are
+ * accumulated in float32, which keeps float32 accuracy.
+ *   lda / ldb / ldd : row pitches in floats (multiples of 4; all bases 16-byte aligned);
+ *   *_stride        : floats between consecutive matrices of a stack (ignored when batch == 1);
+ *   lower_only      : m == n, only the 128 x 128 tiles on or below the diagonal are computed;
+ *   transposed_out  : 0 writes D[i * ldd + j], 1 writes D[j * ldd + i];
+ *   skip_flag       : optional device int; nonzero at run time makes the launch a no-op;
+ *   status_flag     : device int, zeroed by the caller; nonzero afterwards if a bounded wait
+ *                     inside the kernel expired (output undefined, context still usable).
+ * m, n, k need not be multiples of the tile sizes.
+ */
+int qsrtb_gemm3x_tc(const float* a_hi, const float* a_lo, int lda, int64_t a_stride,
+                    const float* b_hi, const float* b_lo, int ldb, int64_t b_stride,
+                    int batch, int m, int n, int k,
+                    float* d, int ldd, int64_t d_stride, float alpha, float beta,
+                    int lower_only, int transposed_out,
+                    const int* skip_flag, int* status_flag, void* stream);
+
+/* Splits `batch` row-major float32 matrices [rows, cols] into their TF32 head and tail planes
+ * (x = hi + lo exactly up to the tail's own rounding), optionally transposing: transpose == 0
+ * gives planes [rows, cols], transpose == 1 planes [cols, rows]; ld_out is the planes' row pitch.
+ * No reference counterpart (operand preparation of qsrtb_gemm3x_tc).
+ */
+int qsrtb_split_tf32(const float* src, int batch, int rows, int cols, int ld, int64_t src_stride,
+                     float* hi, float* lo, int ld_out, int64_t out_stride, int transpose, void* stream);
+
+/* ---- H2: dense Cholesky of the damped Hessian, on the device ------------------------------------
+ * Replaces `torch.linalg.cholesky(H)` inside block_ldl (qsrt/exl3_encoder_backend.py:335) and the
+ * exception the reference catches for its retry loop (:331-370).  In place: on return the lower
+ * triangle of `a` holds L with L L^T = A; the strict upper triangle is scratch.
+ *   workspace : qsrtb_cholesky_workspace_bytes(n) bytes;
+ *   status    : TWO device ints zeroed by the caller.  status[0] = 0, or the 1-based column of the
+ *               first pivot that was not positive (the matrix is not positive definite; the
+ *               contents of `a` are then undefined) - nothing is thrown or trapped, the host reads
+ *               the word when it chooses and adds damping.  status[1] != 0: a bounded wait of the
+ *               tensor-core update expired.
+ * Blocked right-looking factorisation: 128-column panels factored and solved by float32 kernels,
+ * trailing updates by qsrtb_gemm3x_tc.  n is any non-negative size; ld % 4 == 0.
+ */
+int qsrtb_cholesky_workspace_bytes(int n, size_t* bytes);
+int qsrtb_cholesky_blocked(float* a, int n, int ld, void* workspace, size_t workspace_bytes,
+                           int* status, void* stream);
 
 /* ---- H2: Cholesky factor -> unit block-lower LDL feedback factor, in place ---------------
  * Replaces the tail of block_ldl and the diagonal clearing after it
@@ -285,6 +339,26 @@ int qsrtb_records_atoms(int16_t* records, int64_t records_bytes, int tiles_k, in
                         int rate_axis, int n_records, int stripes, const uint8_t* record_bits,
                         int rotation, int64_t atom_pitch_bytes, int16_t* atoms, int64_t atoms_bytes,
                         int to_records, void* stream);
+
+/* ---- C1: routed-error scoring ------------------------------------------------------------------
+ * qsrtb_gated_activation: `gate_up` holds [rows, 2 * inter] pre-activations (gate columns first,
+ * then up: one product of the routed rows against the stacked gate and up matrices); writes the
+ * middle activation act(gate) * up - activation 0 = SiLU (F.silu(gate) * up,
+ * qsrt/glm52_down_construction.py:159-260), 1 = the bounded gated activation of
+ * qsrt/tp_simulator.py:82-93 - as TF32 head / tail planes for qsrtb_gemm3x_tc (hi / lo may both be
+ * NULL) and / or as float32 rows (`middle` may be NULL).
+ *
+ * qsrtb_routed_row_sse: per row r, row_sse[r] = sum_j (candidate[r, j] - reference[r, j])^2 and
+ * (optional) row_energy[r] = sum_j reference[r, j]^2, accumulated in float64: the row reductions of
+ * functional_sse_by_request (qsrt/qsrt_candidates.py:621-654) and _defer_functional_row_sse
+ * (qsrt/pack/qsrt_candidates.py:318-349).  Route weights and request grouping stay with the caller.
+ */
+int qsrtb_gated_activation(const float* gate_up, int64_t rows, int inter, int ld, int activation,
+                           float* hi, float* lo, int ld_planes, float* middle, int ld_middle,
+                           void* stream);
+int qsrtb_routed_row_sse(const float* reference, const float* candidate, int64_t rows, int d,
+                         int ld_reference, int ld_candidate, double* row_sse, double* row_energy,
+                         void* stream);
 
 /* ---- D1: decoder -------------------------------------------------------------------------
  * Replaces unpack_trellis_states + LUT decode (qsrt/qsrt.py:886-913,

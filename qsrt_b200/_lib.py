@@ -22,7 +22,6 @@ _SIGNATURES = {
     "qsrtb_probe_half2_fma": (_c.c_int, [_c.c_int, _PTR, _c.POINTER(_c.c_double), _PTR]),
     "qsrtb_lut_prepare": (_c.c_int, [_PTR, _c.c_int, _PTR, _PTR, _PTR]),
     "qsrtb_viterbi_scratch_bytes": (_c.c_int, [_c.c_int, _c.c_int64, _c.POINTER(_c.c_size_t)]),
-    "qsrtb_viterbi_set_units": (_c.c_int, [_c.c_int]),
     "qsrtb_quantize_tiles": (
         _c.c_int,
         [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_size_t, _PTR],
@@ -52,6 +51,21 @@ _SIGNATURES = {
         [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _PTR, _c.c_int, _c.c_int, _PTR, _c.c_size_t, _PTR, _PTR],
     ),
     "qsrtb_hessian_tc_wait_probe": (_c.c_int, [_PTR, _PTR]),
+    "qsrtb_gemm3x_tc": (
+        _c.c_int,
+        [_PTR, _PTR, _c.c_int, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+         _PTR, _c.c_int, _c.c_int64, _c.c_float, _c.c_float, _c.c_int, _c.c_int, _PTR, _PTR, _PTR],
+    ),
+    "qsrtb_split_tf32": (
+        _c.c_int,
+        [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int64, _c.c_int, _PTR],
+    ),
+    "qsrtb_gated_activation": (
+        _c.c_int, [_PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _c.c_int, _PTR, _c.c_int, _PTR]),
+    "qsrtb_routed_row_sse": (
+        _c.c_int, [_PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR]),
+    "qsrtb_cholesky_workspace_bytes": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_size_t)]),
+    "qsrtb_cholesky_blocked": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _PTR, _c.c_size_t, _PTR, _PTR]),
     "qsrtb_hessian_finish": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _c.c_double, _PTR]),
     "qsrtb_hadamard128": (
         _c.c_int,
@@ -105,8 +119,10 @@ _KERNELS_PER_CALL = {
     "qsrtb_abi_version": 0,
     "qsrtb_last_error": 0,
     "qsrtb_viterbi_scratch_bytes": 0,
-    "qsrtb_viterbi_set_units": 0,
     "qsrtb_hessian_tc_workspace_bytes": 0,
+    "qsrtb_cholesky_workspace_bytes": 0,
+    # per 128-column panel: diagonal block, rows below it, trailing update (the last has only the first)
+    "qsrtb_cholesky_blocked": lambda args: max(0, 3 * ((int(args[1]) + 127) // 128) - 2),
     "qsrtb_hessian_accumulate_tc": 2,
     "qsrtb_col_sumsq": 2,
     "qsrtb_block_ldl_normalize": 3,
@@ -136,7 +152,7 @@ class _Counted:
             return fn
 
         def counted(*args):
-            launch_counts[name] = launch_counts.get(name, 0) + per_call
+            launch_counts[name] = launch_counts.get(name, 0) + (per_call(args) if callable(per_call) else per_call)
             return fn(*args)
 
         return counted

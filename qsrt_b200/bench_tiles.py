@@ -43,17 +43,16 @@ def main() -> None:
     p.add_argument("--units", type=int, default=0, help="work units per thread of the search kernel (0 auto, 1 or 2)")
     args = p.parse_args()
     device = torch.device("cuda:0")
-    tile_api.set_units_per_thread(args.units)
     x = make_tiles(args.family, args.tiles, args.seed).to(device)
     lut = tables.sqg_xor_cheb_t12_bytes(args.bits)
     for _ in range(args.warmup):
-        tile_api.encode_tiles(x, lut, args.bits, args.context)
+        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units)
     torch.cuda.synchronize()
     times = []
     for _ in range(args.iters):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        tile_api.encode_tiles(x, lut, args.bits, args.context)
+        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units)
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))

@@ -75,6 +75,14 @@ def _transform_(matrix: Tensor, axis: int, block_size: int, signs: Tensor | None
     return matrix
 
 
+def _matmul_nt(x: Tensor, w: Tensor) -> Tensor:
+    """``x @ w.T`` in float32 accuracy on the tensor cores."""
+
+    from . import linalg
+
+    return linalg.matmul_nt(x.float().contiguous(), w.float().contiguous())
+
+
 def _as_work_matrix(values: Tensor) -> Tensor:
     if values.ndim != 2 or not torch.is_floating_point(values):
         raise TypeError("block Hadamard input must be a floating point matrix")
@@ -197,7 +205,7 @@ class CoupledHadamardExecution:
         return self._congruence(hessian, 3, self.spec.residual_block_size)
 
     def decode_middle(self, rows: Tensor, w1: Tensor, w3: Tensor, activation: str = "situ") -> Tensor:
-        transformed = torch.cat((rows @ w1.T, rows @ w3.T), dim=1).contiguous()
+        transformed = _matmul_nt(rows, torch.cat((w1, w3), dim=0))
         recovered = _transform_(transformed.float(), 1, self.spec.preactivation_block_size,
                                 self._signs(1, device=rows.device), True)
         gate, up = recovered[:, 0::2], recovered[:, 1::2]
@@ -215,4 +223,4 @@ class CoupledHadamardExecution:
         _validate_triplet(weights)
         transformed_rows = self.transform_inputs(rows)
         middle = self.decode_middle(transformed_rows, weights[0], weights[1], activation)
-        return self.decode_output(middle @ weights[2].T)
+        return self.decode_output(_matmul_nt(middle, weights[2]))

@@ -691,16 +691,17 @@ int check_common(int bits, int tailbite_context, int variant, int64_t n_tiles)
     if (bits < 2 || bits > 4) return qsrtb_fail(QSRTB_EINVAL, "bits must be 2, 3 or 4");
     if (tailbite_context < 1 || tailbite_context > 128)
         return qsrtb_fail(QSRTB_EINVAL, "tailbite_context must be in 1..128");
-    if (variant != 0 && !(variant == 1 && bits == 2))
-        return qsrtb_fail(QSRTB_EINVAL, "variant 1 (dedicated K2 arithmetic) needs bits == 2");
+    if ((variant & ~0x31) != 0 || (variant >> 4) == 3)
+        return qsrtb_fail(QSRTB_EINVAL, "variant: bit 0 selects the dedicated K2 arithmetic, bits 4-5 the thread layout (0, 1 or 2)");
+    if ((variant & 1) && bits != 2)
+        return qsrtb_fail(QSRTB_EINVAL, "variant bit 0 (dedicated K2 arithmetic) needs bits == 2");
     if (n_tiles < 0) return qsrtb_fail(QSRTB_EINVAL, "negative tile count");
     return QSRTB_OK;
 }
 
-// Units per thread of the add-compare-select loop: 2 = 512 threads with half2 labels in
-// registers, 1 = 1024 threads with packed fp8 labels, 0 = the faster of the two as measured
-// on B200 (K2 and K4: 2, K3: 1).  Same results either way.
-int g_units = 0;
+// Units per thread of the add-compare-select loop (bits 4-5 of `variant`): 2 = 512 threads with
+// half2 labels in registers, 1 = 1024 threads with packed fp8 labels, 0 = the faster of the two
+// as measured on B200 (K2 and K4: 2, K3: 1).  Same results either way.
 
 template <int UNITS>
 int dispatch_units(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
@@ -721,7 +722,9 @@ int dispatch_units(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, 
 int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const uint8_t* lut_pm,
              int bits, int context, int variant, void* scratch, size_t scratch_bytes, cudaStream_t s)
 {
-    const int units = g_units != 0 ? g_units : (bits == 3 ? 1 : 2);
+    const int layout = (variant >> 4) & 3;
+    const int units = layout != 0 ? layout : (bits == 3 ? 1 : 2);
+    variant &= 1;
     if (units == 1)
         return dispatch_units<1>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
     return dispatch_units<2>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);
@@ -822,14 +825,6 @@ extern "C" int qsrtb_ldlq_quantize_members(const float* w, const float* comp, fl
                               state_stride, tile_map, tile_map_count, members, scratch, scratch_bytes, stream);
 }
 
-// Tuning knob (not part of the reference interface): units per thread, 1 or 2.
-extern "C" int qsrtb_viterbi_set_units(int units)
-{
-    if (units < 0 || units > 2) return qsrtb_fail(QSRTB_EINVAL, "units per thread must be 0 (auto), 1 or 2");
-    g_units = units;
-    return QSRTB_OK;
-}
-
 // ---- tile search without any allocation ---------------------------------------------------
 //
 // Some hosts of this library may not allocate device memory once they are running: a serving
@@ -855,7 +850,8 @@ uint8_t* g_static_scratch_ptr[kMaxDevices] = {};
 
 // Device address of the array on the current device.  In host code `g_static_scratch` is only
 // a handle for the runtime, not an address a kernel could use; the address is looked up once
-// per device, with that device current, and cached.
+// per device, with that device current, and cached.  Host threads that race on the cache all
+// store the same value for a device, so no lock is taken.
 int static_scratch_for_current_device(uint8_t** out)
 {
     int device = -1;

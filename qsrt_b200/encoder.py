@@ -12,10 +12,13 @@ instead.  The numerical work is done by the hand-written kernels of ``libqsrt_b2
   scatter) in a single launch,
 * ``qsrtb_quantize_tiles`` / ``qsrtb_pack_trellis``.
 
+* ``qsrtb_cholesky_blocked`` - the dense Cholesky inside ``block_ldl`` (panels in float32
+  kernels, trailing updates on the tensor cores, a status word instead of an exception).
+
 PyTorch supplies device memory, streams, the seeded sign draws (which must come from torch's
-CUDA generator to match the reference, ``qsrt/rng.py:16-20``), the dense Cholesky and the
-plain feedback GEMMs (cuBLAS, the very calls the reference issues, which keeps the float32
-rounding of the feedback identical).
+CUDA generator to match the reference, ``qsrt/rng.py:16-20``) and the plain feedback GEMMs
+(cuBLAS, the very calls the reference issues, which keeps the float32 rounding of the feedback
+identical).
 """
 
 from __future__ import annotations
@@ -27,6 +30,7 @@ import threading
 import torch
 
 from . import _lib
+from . import linalg as _linalg
 from . import tiles as _tiles
 from .tiles import _stream_ptr, encode_tiles, prepared_table, quantize_tiles, traceback_scratch, K2_DEDICATED_MAX_LABEL
 
@@ -39,6 +43,12 @@ SIGMA_REG = 0.025
 # pageable memory per 7168-wide Hessian.  With 180 GB of HBM they can stay on the device; set
 # this to False to reproduce the reference's placement exactly.
 KEEP_HESSIAN_ON_DEVICE = True
+
+# Feedback products of the BlockLDLQ recursion: False = the float32 library GEMMs the reference
+# itself calls (same rounding as the reference up to summation order), True = this library's
+# tensor-core products (float32 accuracy from three TF32 products).  ``quant_args["ldlq_tensor_cores"]``
+# overrides it per call.
+LDLQ_TENSOR_CORES = False
 
 finalize_capture_H_mutex = threading.Lock()
 _SHARED_INPUT_SCALES: dict = {}
@@ -175,36 +185,40 @@ def make_shared_h(in_features: int, device: torch.device, hessian: torch.Tensor 
 def block_ldl(H: torch.Tensor, b: int, quant_args: dict, verbose: bool):
     """Block LDL of a damped Hessian (exl3_encoder_backend.py:323-393).
 
-    Returns ``(L, H_cpu)``: ``L`` overwrites H's device storage; a failed Cholesky is retried
-    up to ten times with ``2 * sigma_reg * mean(diag)`` of extra damping, then re-raised.
-    """
+    Returns ``(L, H_copy)``: ``L`` (unit block-lower: identity diagonal blocks, zeros above them)
+    overwrites H's device storage, ``H_copy`` is the matrix that was factored, extra damping
+    included.  The dense Cholesky runs on the device in this library's kernels
+    (``linalg.cholesky_``); a matrix that is not positive definite comes back as a status word, not
+    an exception, and is retried up to ten times with ``2 * sigma_reg * mean(diag)`` of extra
+    damping before ``LinAlgError`` is raised, as in the reference."""
 
     if b != 16:
         raise ValueError("the B200 encoder factors in 16x16 blocks")
     n = H.shape[0]
     assert n % b == 0
+    H_copy = H.clone() if KEEP_HESSIAN_ON_DEVICE else H.cpu()
     retries = 0
     while True:
-        L, info = torch.linalg.cholesky_ex(H)
-        if int(info.item()) == 0:
+        info = _linalg.cholesky_(H)
+        if info == 0:
             break
         retries += 1
         if retries > 10:
             print(" ## Cholesky decomp. failed, number of retries exceeded")
             raise torch.linalg.LinAlgError(
-                f"linalg.cholesky: the input is not positive-definite (leading minor {int(info.item())})"
+                f"linalg.cholesky: the input is not positive-definite (leading minor {info})"
             )
         print(f" !! Cholesky decomp. failed, increasing diagonal damping, attempt {retries}/10")
+        H.copy_(H_copy)   # the failed factorisation left H undefined
         H.diagonal().add_(2.0 * quant_args.get("sigma_reg", SIGMA_REG) * H.diagonal().mean())
-    H_cpu = H.clone() if KEEP_HESSIAN_ON_DEVICE else H.cpu()
-    H.copy_(L)
-    del L
+        H_copy.diagonal().copy_(H.diagonal())
     with torch.cuda.device(H.device):
         _lib.check(
-            _lib.lib().qsrtb_block_ldl_normalize(H.data_ptr(), n, n, _stream_ptr(H.device)),
+            _lib.lib().qsrtb_block_ldl_normalize(H.data_ptr(), n, H.stride(0), _stream_ptr(H.device)),
             "qsrtb_block_ldl_normalize",
         )
-    return H, H_cpu
+    H.diagonal().fill_(1.0)   # identity diagonal blocks (exl3_encoder_backend.py:387-391)
+    return H, H_copy
 
 
 def _prepare_capture_H(H_data: dict, quant_args: dict, verbose: bool):
@@ -243,6 +257,7 @@ def _factor_capture_H(H_data: dict, H: torch.Tensor, su: torch.Tensor, quant_arg
         L = None
     else:
         L, H = block_ldl(H, 16, quant_args, verbose)
+        L.diagonal().zero_()   # exl3_encoder_backend.py:2152-2153
     H_data["L"] = L
     if not KEEP_HESSIAN_ON_DEVICE:
         H = H.cpu()
@@ -660,6 +675,22 @@ def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan,
     encoded = torch.zeros((batch, tiles_k, tiles_n, 256), dtype=torch.short, device=device)
     out["weight_q"], out["encoded"] = weight_q, encoded
 
+    tensor_cores = bool(quant_args.get("ldlq_tensor_cores", LDLQ_TENSOR_CORES))
+    if tensor_cores and (size_k % 4 or buf_size_k % 4):
+        raise ValueError("the tensor-core feedback products need row counts that are multiples of 4")
+    if tensor_cores:
+        # Operands of the feedback products, both stored with the contraction index (a row of the
+        # current span) contiguous: the transposed factor, split once, and the transposed error
+        # rows of the span, split after every 16-row step.  Rows of the span that are not encoded
+        # yet meet zeros of the factor (it is block-lower with empty diagonal blocks), so stale
+        # finite values in the error planes are harmless; the planes start at zero for that reason.
+        factor_t = _linalg.split_tf32(Ls, transpose=True)                       # [B, column, row]
+        err_t = _linalg.Planes(torch.zeros((batch, size_n, buf_size_k), dtype=torch.float, device=device),
+                               torch.zeros((batch, size_n, buf_size_k), dtype=torch.float, device=device))
+
+        def view(planes, rows, cols):
+            return _linalg.Planes(planes.hi[:, rows, cols], planes.lo[:, rows, cols])
+
     def gemm(target, a, b):
         allow = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = tf32
@@ -675,7 +706,11 @@ def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan,
             comp = prod_cache[:, i + bi:i + bj]
             if bj < buf_size_k:
                 # compensation from the rows already encoded inside this span
-                gemm(comp, Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
+                if tensor_cores:
+                    _linalg.gemm_nt(err_t, view(factor_t, slice(i + bi, i + bj), slice(i, j)), comp,
+                                    beta=1.0, transposed_out=True)
+                else:
+                    gemm(comp, Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
             for bits, tile_map in plan((i + bi) // 16):
                 _quantize_rows(
                     weights[:, i + bi:], comp, multiplier, weight_q[:, i + bi:], err[:, i + bi:],
@@ -684,10 +719,18 @@ def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan,
                     comp_ld=size_n, comp_stride=size_k * size_n,
                     state_stride=tiles_k * tiles_n * 256, tile_map=tile_map,
                 )
+            if tensor_cores:
+                _linalg.split_tf32(err[:, i + bi:i + bj], transpose=True,
+                                   out=view(err_t, slice(None), slice(bi, bj)))
             if bj == 16 and i > 0:
                 # cache the span's error for every row block still to be encoded
-                gemm(prod_cache[:, :i], Ls[:, i:j, :i].transpose(1, 2), err[:, i:j])
+                if tensor_cores:
+                    _linalg.gemm_nt(view(factor_t, slice(0, i), slice(i, j)), err_t, prod_cache[:, :i], beta=1.0)
+                else:
+                    gemm(prod_cache[:, :i], Ls[:, i:j, :i].transpose(1, 2), err[:, i:j])
             yield
+    if tensor_cores:
+        _linalg.check_status(device)
 
 
 def _ldlq_core(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan, pb=None):

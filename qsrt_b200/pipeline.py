@@ -74,15 +74,16 @@ def situ(gate: torch.Tensor, up: torch.Tensor, *, beta: float = 4.0, linear_beta
 
 def gated_middle(rows: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, activation: str = "silu",
                  execution=None) -> torch.Tensor:
+    """Middle activation ``act(x W1^T) * (x W3^T)`` of routed rows: one tensor-core product against
+    the stacked gate / up matrices and the fused activation kernel (``scoring.gated_middle``)."""
+
     if execution is not None:
         return execution.decode_middle(rows, w1, w3, activation)
-    gate = rows @ w1.T
-    up = rows @ w3.T
-    if activation == "silu":
-        return torch.nn.functional.silu(gate) * up
-    if activation == "situ":
-        return situ(gate, up)
-    raise ValueError(f"unknown activation {activation!r}")
+    if activation not in ("silu", "situ"):
+        raise ValueError(f"unknown activation {activation!r}")
+    from . import scoring
+
+    return scoring.gated_middle(rows, w1, w3, activation)
 
 
 def quant_args_for(bits: int, device: torch.device, *, seed: int, sv_seed: int, sigma_reg: float = encoder.SIGMA_REG,
@@ -204,20 +205,34 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
         gate_up = [(_payload(a_out[2 * i], a_args[2 * i]), _payload(a_out[2 * i + 1], a_args[2 * i + 1]))
                    for i in range(len(experts))]
 
-    for ex, (p1, p3), res, args, w, middle, info in zip(experts, gate_up, down_out, down_args, weights_sq, middles, evidence):
+    scores = []
+    for ex, (p1, p3), res, args, info in zip(experts, gate_up, down_out, down_args, evidence):
         p2 = _payload(res, args)
         payload = ExpertPayload(ex.expert_id, bits, p1, p3, p2, evidence=info)
         payload.payload_bytes = sum(p.trellis.numel() * 2 + p.suh.numel() * 2 + p.svh.numel() * 2 for p in (p1, p3, p2))
         if score:
-            source_middle = middle if not down_from_reconstruction else gated_middle(
-                ex.rows.float(), ex.w1.float(), ex.w3.float(), activation)
-            teacher = source_middle @ ex.w2.float().T
-            decoded_mid = gated_middle(ex.rows.float(), decode_matrix(p1), decode_matrix(p3), activation)
-            student = decoded_mid @ decode_matrix(p2).T
-            payload.routed_sse = float(((student - teacher).double().square().sum(dim=1) * w.double()).sum())
-            payload.routed_energy = float((teacher.double().square().sum(dim=1) * w.double()).sum())
+            scores.append(score_payload(ex, payload, activation))
         results.append(payload)
+    # one host synchronisation for the whole batch (the reference defers its row sums the same way,
+    # qsrt/pack/qsrt_candidates.py:318-349)
+    if scores:
+        values = torch.stack([torch.stack(pair) for pair in scores]).cpu()
+        for payload, (sse, energy) in zip(results, values.tolist()):
+            payload.routed_sse, payload.routed_energy = sse, energy
     return results
+
+
+def score_payload(source: ExpertSource, payload: ExpertPayload, activation: str = "silu"):
+    """Routed functional error of a stored expert candidate: its three packed matrices are decoded
+    and run against the source expert on the expert's routed rows
+    (``sum_rows gate^2 ||student - teacher||^2``; ``functional_sse_by_request`` summed over the
+    requests, qsrt/qsrt_candidates.py:621-654).  Returns ``(sse, energy)`` as 0-d float64 device
+    tensors; nothing synchronises."""
+
+    from . import scoring
+
+    decoded = (decode_matrix(payload.w1), decode_matrix(payload.w3), decode_matrix(payload.w2))
+    return scoring.routed_output_sse(source.rows, source.gates, (source.w1, source.w3, source.w2), decoded, activation)
 
 
 def _encode_coupled_batch(experts, spec, *, score, activation, **kwargs):
@@ -231,15 +246,21 @@ def _encode_coupled_batch(experts, spec, *, score, activation, **kwargs):
         moved.append(_CoupledSource(c1, c3, c2, rows, ex.gates, ex.expert_id, execution, activation))
         executions.append(execution)
         if score:
-            teachers.append(gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation) @ ex.w2.float().T)
+            from . import linalg
+
+            teachers.append(linalg.matmul_nt(gated_middle(ex.rows.float(), ex.w1.float(), ex.w3.float(), activation),
+                                             ex.w2.float().contiguous()))
     payloads = encode_expert_batch(moved, score=False, activation=activation, **kwargs)
     if score:
         for payload, src, execution, teacher, ex in zip(payloads, moved, executions, teachers, experts):
+            from . import scoring
+
             decoded = (decode_matrix(payload.w1), decode_matrix(payload.w3), decode_matrix(payload.w2))
             student = execution.execute(ex.rows.float(), decoded, activation)
             w = ex.gates.float().square().double()
-            payload.routed_sse = float(((student - teacher).double().square().sum(dim=1) * w).sum())
-            payload.routed_energy = float((teacher.double().square().sum(dim=1) * w).sum())
+            sse, energy = scoring.row_sse(teacher, student, energy=True)
+            payload.routed_sse = float((sse * w).sum())
+            payload.routed_energy = float((energy * w).sum())
     return payloads
 
 
@@ -266,7 +287,8 @@ class LayerSelection:
 
 
 def encode_layer_mixed(experts: list[ExpertSource], *, layer_experts: int, device: torch.device,
-                       budget_bpw: float = 3.083333, group=None, **encode_kwargs) -> LayerSelection:
+                       budget_bpw: float = 3.083333, group=None, experts_per_batch: int = 4,
+                       **encode_kwargs) -> LayerSelection:
     """Mixed-rate candidate selection around a K3 baseline.
 
     Every local expert is encoded completely at K2, K3 and K4; the routed functional error and
@@ -274,15 +296,24 @@ def encode_layer_mixed(experts: list[ExpertSource], *, layer_experts: int, devic
     (``selection.gather_candidate_table``, the path's only collective); every rank then runs the
     same greedy equal-byte K2<->K4 exchange (``selection.equal_byte_exchange``) under the
     trellis budget (3.083333 bpw = all-K3 plus one expert in twelve raised to K4); the selected
-    payloads are checked by decoding their packed bitstreams back to E4M3.
+    payloads are checked by decoding their packed bitstreams back to E4M3.  ``experts`` is a
+    list or any sequence with ``len()`` and slicing that yields ``ExpertSource`` items (they are
+    taken ``experts_per_batch`` at a time, so a lazy sequence keeps only one batch resident).
     """
 
     from . import selection
 
     rates = (2, 3, 4)
     device = torch.device(device)
-    by_rate = {b: encode_expert_batch(experts, bits=b, device=device, score=True, **encode_kwargs) for b in rates}
-    local_ids = [ex.expert_id for ex in experts]
+    # experts go through the encoder a few at a time (an expert of the full layer shape holds
+    # about 1 GB of Hessians and factors while it is being encoded)
+    step = max(1, int(experts_per_batch))
+    by_rate = {b: [] for b in rates}
+    for begin in range(0, len(experts), step):
+        for b in rates:
+            by_rate[b].extend(encode_expert_batch(experts[begin:begin + step], bits=b, device=device, score=True,
+                                                  **encode_kwargs))
+    local_ids = [payload.expert_id for payload in by_rate[rates[0]]]
     local = torch.empty((len(experts), 3, 2), dtype=torch.float64, device=device)
     for c, b in enumerate(rates):
         for i, payload in enumerate(by_rate[b]):
@@ -296,12 +327,12 @@ def encode_layer_mixed(experts: list[ExpertSource], *, layer_experts: int, devic
     free_upgrades = int(round((budget_bpw - 3.0) * layer_experts + 1e-9))
     allocation = selection.equal_byte_exchange(table, free_upgrades=max(0, free_upgrades))
     chosen = {}
-    for i, ex in enumerate(experts):
-        payload = by_rate[allocation.bits[ex.expert_id]][i]
+    for i, expert_id in enumerate(local_ids):
+        payload = by_rate[allocation.bits[expert_id]][i]
         for matrix in (payload.w1, payload.w3, payload.w2):
             if not verify_payload_roundtrip(matrix):
-                raise RuntimeError(f"expert {ex.expert_id}: packed payload failed its decode round trip")
-        chosen[ex.expert_id] = payload
+                raise RuntimeError(f"expert {expert_id}: packed payload failed its decode round trip")
+        chosen[expert_id] = payload
     k3_bytes = float(table[:, 1, 1].sum())
     return LayerSelection(allocation.bits, table, chosen, allocation.total_sse, allocation.baseline_sse,
                           allocation.exchanges, 3.0 * allocation.total_bytes / k3_bytes)

@@ -60,13 +60,6 @@ def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-def set_units_per_thread(units: int) -> None:
-    """Tuning knob of the search kernel: 2 (512 threads, half2 labels in registers),
-    1 (1024 threads, packed fp8 labels) or 0 (per-rate default).  Results do not depend on it."""
-
-    _lib.check(_lib.lib().qsrtb_viterbi_set_units(int(units)), "qsrtb_viterbi_set_units")
-
-
 def prepared_table(codebook: torch.Tensor, bits: int, device: torch.device):
     """Device copies of a state-indexed table: (state order, predecessor-major order, amax)."""
 
@@ -118,8 +111,13 @@ def encode_tiles(
     tailbite_context: int = 128,
     *,
     force_generic: bool = False,
+    units_per_thread: int = 0,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """Encode ``[N, 256]`` float32 CUDA tiles with a state-indexed E4M3 table."""
+    """Encode ``[N, 256]`` float32 CUDA tiles with a state-indexed E4M3 table.
+
+    ``units_per_thread`` picks the search kernel's thread layout for this call (0 = per-rate
+    default, 1 = 1024 threads with fp8 labels, 2 = 512 threads with half2 labels); the results
+    do not depend on it."""
 
     if not tiles.is_cuda:
         raise ValueError("input_tiles must be CUDA")
@@ -129,6 +127,8 @@ def encode_tiles(
         raise ValueError("the B200 tile encoder supports K2, K3 and K4")
     if not 1 <= int(tailbite_context) <= 128:
         raise ValueError("tailbite_context must be in 1..128")
+    if units_per_thread not in (0, 1, 2):
+        raise ValueError("units_per_thread must be 0 (per-rate default), 1 or 2")
     tiles = tiles.contiguous()
     device = tiles.device
     lut, lut_pm, abs_max = prepared_table(codebook, bits, device)
@@ -147,7 +147,7 @@ def encode_tiles(
         _lib.check(
             _lib.lib().qsrtb_quantize_tiles(
                 tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits,
-                int(tailbite_context), 1 if dedicated else 0, output.data_ptr(),
+                int(tailbite_context), (1 if dedicated else 0) | (int(units_per_thread) << 4), output.data_ptr(),
                 indices.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream_ptr(device),
             ),
             "qsrtb_quantize_tiles",

@@ -2,17 +2,16 @@
 
 from __future__ import annotations
 
-import importlib.util
 import math
-import sys
-from functools import lru_cache
 from pathlib import Path
 
 import numpy as np
 import torch
 
+from oracle import ref_kernel
+
 ROOT = Path(__file__).resolve().parents[1]
-REF_EXT = ROOT / "oracle" / "_ref" / "qsrt_ref_sqg_ext.so"
+REF_EXT = ref_kernel.REF_EXT
 FAMILIES = ("normal", "scaled", "heavy", "spike")
 
 
@@ -51,38 +50,23 @@ def mixed_tiles(per_family: int, seed: int) -> torch.Tensor:
     return torch.cat(parts + [extra]).contiguous()
 
 
-@lru_cache(maxsize=1)
 def reference_extension():
     """The UNMODIFIED reference CUDA extension built by oracle/build_ref.py, or None."""
 
-    if not REF_EXT.exists():
-        return None
-    spec = importlib.util.spec_from_file_location("qsrt_ref_sqg_ext", REF_EXT)
-    module = importlib.util.module_from_spec(spec)
-    sys.modules["qsrt_ref_sqg_ext"] = module
-    spec.loader.exec_module(module)
-    return module
+    return ref_kernel.reference_extension()
+
+
+_reference_searches: dict = {}
 
 
 def reference_quantize_tiles(tiles: torch.Tensor, lut_state: torch.Tensor, bits: int, context: int):
     """Drive the reference kernel exactly as qsrt/sqg_quantizer.py:607-651 does."""
 
-    ext = reference_extension()
-    device = tiles.device
-    edges = 65536 >> bits
-    decisions = edges // 4 if bits == 2 else edges // 2 if bits <= 4 else edges
-    sms = torch.cuda.get_device_properties(device).multi_processor_count
-    max_batch = max(256, 3 * sms)
-    costs = torch.zeros((max_batch, 2, edges), dtype=torch.float16, device=device)
-    trace = torch.empty((max_batch, 256, decisions), dtype=torch.uint8, device=device)
-    lut = lut_state.to(device=device, dtype=torch.uint8).contiguous()
-    abs_max = float(lut.view(torch.float8_e4m3fn).float().abs().amax())
-    if bits in (2, 3, 4):
-        lut = lut.reshape(1 << bits, edges // 2, 2).permute(1, 0, 2).contiguous().reshape(-1)
-    out = torch.empty_like(tiles)
-    idx = torch.empty_like(tiles, dtype=torch.int16)
-    ext.quantize_tiles_sqg(tiles.contiguous(), out, idx, costs, trace, lut, bits, context, abs_max)
-    torch.cuda.synchronize(device)
+    key = (str(tiles.device), bits, context, lut_state.data_ptr())
+    if key not in _reference_searches:
+        _reference_searches[key] = (lut_state, ref_kernel.ReferenceTileSearch(lut_state, bits, context, tiles.device))
+    out, idx = _reference_searches[key][1](tiles)
+    torch.cuda.synchronize(tiles.device)
     return out, idx
 
 
@@ -313,3 +297,61 @@ def tile_digests(states) -> np.ndarray:
     flat = np.ascontiguousarray(np.asarray(states).reshape(-1, 256).astype(np.int16))
     return np.array([int.from_bytes(hashlib.blake2b(row.tobytes(), digest_size=8).digest(), "little") for row in flat],
                     dtype=np.uint64)
+
+
+# ---- teacher-forced replay of the reference's BlockLDLQ recursion on the device ---------------------
+def teacher_forced_replay(weight_r: torch.Tensor, factor: torch.Tensor, forced_weight_q: torch.Tensor, *,
+                          tile_search, order: torch.Tensor, buf_size_k: int = 128):
+    """Walk the reverse block recursion of ``ldlq`` (qsrt/exl3_encoder_backend.py:470-539) with the
+    reference's own call shapes - ``addmm_`` of the in-span factor slice per 16-row block, one
+    ``addmm_`` of the whole span afterwards - but with the history taken from ``forced_weight_q``
+    (the regularised-domain reconstruction somebody else produced), so that a differing tile does
+    not compound.  ``tile_search(tiles [n, 256] in tensor-core order) -> states [n, 256] int16``.
+    Returns ``(states [k/16, n/16, 256] int16, targets [k, n] float32)``: what the reference's
+    loop would have encoded at every step, and the encoder inputs it would have seen."""
+
+    size_k, size_n = weight_r.shape
+    tiles_n = size_n // 16
+    device = weight_r.device
+    prod_cache = torch.zeros((size_k, size_n), dtype=torch.float32, device=device)
+    states = torch.zeros((size_k // 16, tiles_n, 256), dtype=torch.int16, device=device)
+    targets = torch.empty_like(weight_r)
+    allow = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for j in range(size_k, 0, -buf_size_k):
+            i = j - buf_size_k
+            b_weight, b_weight_q = weight_r[i:j], forced_weight_q[i:j]
+            b_factor = factor[i:j]
+            for bj in range(buf_size_k, 0, -16):
+                bi = bj - 16
+                compensation = prod_cache[i + bi:i + bj]
+                compensation.addmm_(b_factor[bj:, i + bi:i + bj].T, b_weight[bj:] - b_weight_q[bj:])
+                rows = b_weight[bi:bj] + compensation
+                targets[i + bi:i + bj] = rows
+                tiles = rows.reshape(16, tiles_n, 16).permute(1, 0, 2).reshape(tiles_n, 256)[:, order].contiguous()
+                states[(i + bi) // 16] = tile_search(tiles)
+            prod_cache.addmm_(b_factor.T, b_weight - b_weight_q)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = allow
+    return states, targets
+
+
+# ---- routed-error scoring cases -------------------------------------------------------------------
+SCORING_REQUESTS = {3: "doc-a", 7: "doc-b", 8: "doc-c"}
+
+
+def scoring_inputs(seed: int = 1618, rows: int = 96, hidden: int = 512, inter: int = 256):
+    """Seeded expert triplet, a perturbed candidate triplet, routed rows, gates and request epochs
+    (CPU float32).  Hidden 512 and intermediate 256 admit the coupled 512 / 128 / 128 blocks."""
+
+    g = torch.Generator().manual_seed(seed)
+    source = (torch.randn((inter, hidden), generator=g) * 0.05, torch.randn((inter, hidden), generator=g) * 0.05,
+              torch.randn((hidden, inter), generator=g) * 0.05)
+    candidates = {}
+    for name, noise in (("fine", 0.002), ("coarse", 0.01)):
+        candidates[name] = tuple(w + noise * torch.randn(w.shape, generator=g) for w in source)
+    x = torch.randn((rows, hidden), generator=g) * torch.exp(0.3 * torch.randn(hidden, generator=g))
+    gates = torch.rand(rows, generator=g) * 0.5 + 0.05
+    steps = torch.tensor([sorted(SCORING_REQUESTS)[i % 3] for i in range(rows)], dtype=torch.int64)
+    return source, candidates, x, gates, steps

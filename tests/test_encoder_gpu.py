@@ -72,13 +72,13 @@ def test_block_ldl_reconstructs_hessian(cuda_device):
     factor, h_cpu = encoder.block_ldl(h.to(cuda_device).clone(), 16, {"sigma_reg": 0.01}, False)
     factor = factor.cpu().double()
     ref_factor, _ = eo.block_ldl(h.numpy(), 16, 0.01)
-    ref_factor[np.diag_indices_from(ref_factor)] = 0
-    for i in range(16):
-        ref_factor[i * 16:(i + 1) * 16, i * 16:(i + 1) * 16] = 0
+    for i in range(16):   # unit block-lower: identity diagonal blocks, as the reference returns it
+        ref_factor[i * 16:(i + 1) * 16, i * 16:(i + 1) * 16] = np.eye(16)
     assert _rel(factor.numpy(), ref_factor) < 1e-4
-    # H = (L + I) D (L + I)^T with D = DL DL^T taken from the Cholesky factor
+    assert np.array_equal(np.triu(factor.numpy(), 1), np.zeros((256, 256)))
+    # H = L D L^T with D = DL DL^T taken from the Cholesky factor
     chol = torch.linalg.cholesky(h.double())
-    unit = factor + torch.eye(256, dtype=torch.float64)
+    unit = factor
     d = torch.zeros_like(unit)
     for i in range(16):
         blk = chol[i * 16:(i + 1) * 16, i * 16:(i + 1) * 16]
@@ -251,27 +251,37 @@ def test_g_scale_search_matches_oracle(cuda_device):
 
 
 def test_uniform_batch_matches_single_calls(cuda_device):
-    """Stacked distinct-Hessian batch == the same tensors encoded one by one."""
+    """Stacked distinct-Hessian batch == the same tensors encoded one by one.
+
+    Both entry points search the global scale themselves (the batch API has no override, as in
+    the reference); the search of a tensor does not depend on what else is in the batch, so the
+    scales and the stored scale vectors must be equal to the last bit.  The tile grids are compared
+    payload against payload: the stacked recursion issues its feedback products as one batched
+    GEMM, for which the reference promises no bit-exact grouping
+    (qsrt/exl3_encoder_backend.py:1213-1221), hence a 97 % floor instead of equality."""
 
     outs_single, outs_batch = [], None
-    weights, h_datas, args_list = [], [], []
+    weights, h_datas, args_list, single_args = [], [], [], []
     for e in range(3):
         gate, hessian = _tiny_expert(1100 + e)
         hessian = hessian * (1.0 + 0.1 * e)
         w = gate.T.contiguous().to(cuda_device)
-        args = _quant_args(3, cuda_device, g_scale_override=0.85)
+        args = _quant_args(3, cuda_device)
         _, proxy, tensors = encoder.quantize_qsrt(w.clone(), encoder.make_shared_h(512, cuda_device, hessian), args, False)
         outs_single.append((proxy, tensors))
+        single_args.append(args)
         weights.append(w.clone())
         h_datas.append(encoder.make_shared_h(512, cuda_device, hessian))
-        args_list.append(_quant_args(3, cuda_device, g_scale_override=0.85))
-    # quantize_uniform_batch searches scales itself; force the same scale through the override
-    # by comparing payloads only where the searched scale is not involved
+        args_list.append(_quant_args(3, cuda_device))
     outs_batch = encoder.quantize_uniform_batch(weights, h_datas, args_list)
-    for (p1, t1), (p2, t2), qa in zip(outs_single, outs_batch, args_list):
-        assert t2["trellis"].shape == t1["trellis"].shape
-        assert torch.equal(t2["svh"].abs() > 0, t1["svh"].abs() > 0)
-        assert 0.0 < p2 < 1.0 and qa["g_scale"] > 0
+    for (p1, t1), (p2, t2), qa, qa1 in zip(outs_single, outs_batch, args_list, single_args):
+        assert qa["g_scale"] == qa1["g_scale"]
+        assert torch.equal(t2["suh"], t1["suh"]) and torch.equal(t2["svh"], t1["svh"])
+        assert t2["trellis"].shape == t1["trellis"].shape and t2["trellis"].dtype == torch.int16
+        same = (t2["trellis"] == t1["trellis"]).all(dim=-1).float().mean().item()
+        print("batched vs single tile identity", same)
+        assert same >= 0.97, f"payload tile identity {same:.4f}"
+        assert abs(p2 / p1 - 1.0) < 1e-2
 
 
 def test_mixed_rate_k_axis_matches_uniform_when_constant(cuda_device):
@@ -337,14 +347,20 @@ def test_quantize_qsrt_batch_candidates(cuda_device):
 
 
 # ---- quantize_qsrt against runs of the reference's own encoder code ---------------------------------
+# Free-running tile identity every case must reach (1.0 unless named): see the test's docstring.
+REFERENCE_RUN_IDENTITY_FLOOR = {"k3_1024_tiles_scale_search": 0.975}
+
+
 @pytest.mark.parametrize("name", list(helpers.ENCODER_CASES))
 def test_quantize_qsrt_against_reference_run(cuda_device, monkeypatch, name):
     """tests/golden/encoder_golden.npz holds what qsrt/exl3_encoder_backend.py itself produced for
     these seeded inputs (run on the CPU around the pinned tile search).  The sign vectors are
     device-generator draws in the reference, so the golden's are injected; everything else is the
-    product path.  Scale vectors agree to the last fp16 bit up to rounding of the float32 RMS sums,
-    the free-running tile grid to >= 85 % (one near-tie flip re-routes the rows above it) and the
-    proxy error to 1 %."""
+    product path.  Scale vectors agree to the last fp16 bit up to rounding of the float32 RMS sums.
+    Free-running, the six cases of 64-128 tiles must reproduce the reference's packed trellis
+    tile for tile; the 1024-tile case keeps >= REFERENCE_RUN_IDENTITY_FLOOR (measured 98.1 %: one
+    near-tie decided differently by the float32 feedback GEMM re-routes the rows encoded after it)
+    and its reconstruction error must agree with the reference run's to 0.1 %."""
 
     from pathlib import Path
 
@@ -391,7 +407,79 @@ def test_quantize_qsrt_against_reference_run(cuda_device, monkeypatch, name):
         want_states = oracle.unpack_trellis_states(golden[f"{name}_trellis"].reshape(-1, 16 * bits), bits)
         same = (got_states == want_states).all(axis=-1)
         print(name, "tile identity", float(same.mean()), "proxy", proxy, want_proxy)
-        assert same.mean() >= 0.85, f"tile identity {same.mean():.4f}"
+        floor = REFERENCE_RUN_IDENTITY_FLOOR.get(name, 1.0)
+        assert same.mean() >= floor, f"tile identity {same.mean():.4f} below {floor}"
         want = golden[f"{name}_weight_q_probe"]
         got = (vector @ weight_q).cpu().numpy()
         assert np.linalg.norm(got - want) <= (1e-4 if same.all() else 0.2) * np.linalg.norm(want)
+        # reconstruction error of the stored payloads, both decoded by the same restatement
+        lut = tables.sqg_xor_cheb_t12_bytes(bits).numpy()
+        grid = (k // 16, n // 16, 256)
+        ours = oracle.decode_weight(got_states.reshape(grid), tensors["suh"].cpu().numpy(),
+                                    tensors["svh"].cpu().numpy(), lut)
+        theirs = oracle.decode_weight(want_states.reshape(grid), golden[f"{name}_suh"], golden[f"{name}_svh"], lut)
+        source = weight.numpy().astype(np.float64)
+        mse_ours = float(((ours - source) ** 2).mean())
+        mse_theirs = float(((theirs - source) ** 2).mean())
+        print(name, "reconstruction mse", mse_ours, mse_theirs, mse_ours / mse_theirs - 1.0)
+        assert abs(mse_ours / mse_theirs - 1.0) <= 1e-3, (mse_ours, mse_theirs)
+
+
+# ---- full-size teacher-forced identity against the unmodified reference kernel -------------------------
+def _full_size_case(device, bits):
+    """One gate-shaped matrix of the full layer ([in 7168, out 2048]) and a routed-rows Hessian
+    (1536 rows: rank-deficient before damping, like the layer's average expert)."""
+
+    g = torch.Generator().manual_seed(31000 + bits)
+    weight = (torch.randn((7168, 2048), generator=g) * 0.02).to(device)
+    gd = torch.Generator(device=device).manual_seed(31001)
+    rows = torch.randn((1536, 7168), generator=gd, device=device)
+    rows *= torch.exp(0.5 * torch.randn(7168, generator=gd, device=device))
+    hessian = (rows.T @ rows / rows.shape[0]).float()
+    return weight, hessian
+
+
+def _teacher_forced_against_reference_kernel(device, bits, **extra_args):
+    if helpers.reference_extension() is None:
+        pytest.skip("the reference tile-encoder extension (oracle/_ref) is not built")
+    weight, hessian = _full_size_case(device, bits)
+    args = _quant_args(bits, device, sigma_reg=0.025, **extra_args)
+    h_data = encoder.make_shared_h(7168, device, hessian)
+    del hessian
+    _, proxy, tensors = encoder.quantize_qsrt(weight, h_data, args, False)
+    lut = args["sqg_e4m3_lut"]
+    states = codec.unpack_trellis_states(tensors["trellis"], bits)
+    history = codec.decode_regularized_weight(states, lut=lut)      # reconstruction in work coordinates
+    ref_states, targets = helpers.teacher_forced_replay(
+        weight, h_data["L"], history,                               # `weight` was regularised in place
+        tile_search=lambda tiles: helpers.reference_quantize_tiles(tiles, lut, bits, 128)[1],
+        order=encoder.tensor_core_perm(device).long())
+    same = (states == ref_states).all(dim=-1)
+    identity = float(same.float().mean())
+    differing = int((~same).sum())
+    worst = 0.0
+    if differing:
+        tiles = helpers.matrix_to_tc_tiles(targets, encoder.tensor_core_perm(device).long()).reshape(same.shape + (256,))
+        pick = (~same).nonzero()[:256]
+        t = tiles[pick[:, 0], pick[:, 1]].cpu().numpy()
+        clamp = 64.0 if bits == 2 else None
+        ours = oracle.path_cost(t, states[pick[:, 0], pick[:, 1]].cpu().numpy(), lut.numpy(), clamp)
+        theirs = oracle.path_cost(t, ref_states[pick[:, 0], pick[:, 1]].cpu().numpy(), lut.numpy(), clamp)
+        worst = float(np.max(np.abs(ours - theirs) / np.maximum(theirs, 1e-12)))
+    print(f"K{bits} full-size teacher-forced: {same.numel()} tiles, identity {identity:.6f}, "
+          f"{differing} differ, worst relative path-cost gap {worst:.3e}, proxy {proxy:.5f}")
+    return identity, worst
+
+
+@pytest.mark.parametrize("bits", [3, 2])
+def test_full_size_teacher_forced_identity_vs_reference_kernel(cuda_device, bits):
+    """All 57 344 tiles of a [7168, 2048] matrix: the reference's own recursion
+    (qsrt/exl3_encoder_backend.py:470-539, its ``addmm_`` shapes, the unmodified reference CUDA
+    kernel as tile search) is replayed on the product's history.  >= 99.9 % of the tiles must be
+    bit-identical; a differing tile saw an encoder input that differs by float32 summation order
+    of the feedback product (one fp16 ulp after rounding), and its path cost, evaluated in float64
+    on the replay's input, must be within 2e-3 relative of the reference's."""
+
+    identity, worst = _teacher_forced_against_reference_kernel(cuda_device, bits)
+    assert identity >= 0.999, f"tile identity {identity:.5f}"
+    assert worst <= 2e-3

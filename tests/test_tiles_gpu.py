@@ -105,15 +105,10 @@ def test_thread_layouts_agree(cuda_device, bits):
 
     tiles = helpers.mixed_tiles(5, seed=31 + bits).to(cuda_device)
     lut = _lut(bits)
-    try:
-        tile_api.set_units_per_thread(1)
-        out1, idx1 = tile_api.encode_tiles(tiles, lut, bits, 128)
-        gen1 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True)
-        tile_api.set_units_per_thread(2)
-        out2, idx2 = tile_api.encode_tiles(tiles, lut, bits, 128)
-        gen2 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True)
-    finally:
-        tile_api.set_units_per_thread(0)
+    out1, idx1 = tile_api.encode_tiles(tiles, lut, bits, 128, units_per_thread=1)
+    gen1 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True, units_per_thread=1)
+    out2, idx2 = tile_api.encode_tiles(tiles, lut, bits, 128, units_per_thread=2)
+    gen2 = tile_api.encode_tiles(tiles, lut, bits, 32, force_generic=True, units_per_thread=2)
     assert torch.equal(idx1, idx2) and torch.equal(out1, out2)
     assert torch.equal(gen1[1], gen2[1])
     ref_out, ref_idx = oracle.quantize_tiles(tiles.cpu().numpy()[:8], lut.numpy(), bits, 128)

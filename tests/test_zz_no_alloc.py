@@ -42,12 +42,25 @@ def test_static_scratch_entry_matches_regular_entry_twice(cuda_device, bits):
     first = torch.randn((70, 256), generator=g)
     first[5] *= 100.0            # saturating row: takes the re-encode path of the generic arithmetic
     second = torch.randn((33, 256), generator=g) * 2.0
-    for batch, context in ((first, 128), (second, 32)):
+    for call, (batch, context) in enumerate(((first, 128), (second, 32))):
         tiles = batch.to(cuda_device).contiguous()
         expected_out, expected_states = tile_api.encode_tiles(tiles, codebook, bits, context)
-        status, out, states = _static_encode(tiles, lut, lut_pm, bits, context, variant)
+        torch.cuda.synchronize(cuda_device)
+        out = torch.empty_like(tiles)
+        states = torch.empty_like(tiles, dtype=torch.int16)
+        free_before, _ = torch.cuda.mem_get_info(cuda_device)
+        held_before = torch.cuda.memory_allocated(cuda_device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+        status = _lib.lib().qsrtb_quantize_tiles_static(
+            tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits, context, variant,
+            out.data_ptr(), states.data_ptr(), stream)
         assert status == _lib.OK, _lib.lib().qsrtb_last_error()
         torch.cuda.synchronize(cuda_device)
+        if call == 1:
+            # Once the first call on this device has made the library's module resident, a call
+            # leaves the device's free memory and the caller's pool exactly as it found them.
+            assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
+            assert torch.cuda.memory_allocated(cuda_device) == held_before
         assert torch.equal(states, expected_states)
         assert torch.equal(out, expected_out)
 
