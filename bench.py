@@ -502,8 +502,8 @@ def run_b200(args) -> None:
         "steps_timed": steps,
         "covers_layer": steps >= len(groups),
         "rank_pass_s": [v / 1e3 for v in pass_values] if steps >= len(groups) else None,
-        "step_ms_min": min(b - a for a, b in zip([0.0] + per_step[:-1], per_step)),
-        "step_ms_max": max(b - a for a, b in zip([0.0] + per_step[:-1], per_step)),
+        "step_ms": [round(b - a, 1) for a, b in zip([0.0] + per_step[:-1], per_step)],
+        "step_rows": [sum(layer.row_counts[e] for e in group_of(i)) for i in range(steps)],
     }
     line = {
         "metric": "MoE-layer encode Mweights/s",

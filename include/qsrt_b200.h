@@ -145,6 +145,19 @@ int qsrtb_hadamard128(float* x, int batch, int rows, int cols, int ld, int64_t x
 int qsrtb_signed_block_hadamard(float* x, int64_t rows, int cols, int ld, int axis, int block_size,
                                 const float* signs, int sign_after, void* stream);
 
+/* The same "D H" transform along the input axis (axis 1) with the source matrix read in its
+ * packed MXFP4 storage - packed [rows, cols / 2] E2M1 codes, low nibble first, scale
+ * [rows, cols / 32] E8M0 bytes (dequant law of qsrt/io/mxfp4.py:50-63) - so that source ingest and
+ * the first coupled transform (qsrt/qsrt_coupled.py:145-196) are one pass and the dequantised
+ * matrix is never stored.  Source row r goes to output row r * row_step + row_offset (row_step 2
+ * interleaves the gate and up matrices); round_bf16 != 0 rounds every dequantised value to
+ * bfloat16 first, as a bf16 checkpoint of the source holds it.  Results equal dequant followed by
+ * qsrtb_signed_block_hadamard bit for bit.
+ */
+int qsrtb_mxfp4_signed_block_hadamard(const uint8_t* packed, const uint8_t* scale, int64_t rows, int cols,
+                                      float* out, int ld, int row_step, int row_offset, int block_size,
+                                      const float* signs, int round_bf16, void* stream);
+
 /* Column sums of squares of `batch` matrices (the out-channel RMS of regularize,
  * qsrt/exl3_encoder_backend.py:2508-2521, 2634).  workspace: batch*ceil(rows/256)*cols floats. */
 int qsrtb_col_sumsq(const float* x, int batch, int rows, int cols, int ld, int64_t x_stride,
@@ -195,7 +208,7 @@ int qsrtb_split_tf32(const float* src, int batch, int rows, int cols, int ld, in
  *               the word when it chooses and adds damping.  status[1] != 0: a bounded wait of the
  *               tensor-core update expired.
  * Blocked right-looking factorisation: 128-column panels factored and solved by float32 kernels,
- * trailing updates by qsrtb_gemm3x_tc.  n is any non-negative size; ld % 4 == 0.
+ * trailing updates by qsrtb_gemm3x_tc.  n % 16 == 0 (the block size of the block-LDL factor); ld % 4 == 0.
  */
 int qsrtb_cholesky_workspace_bytes(int n, size_t* bytes);
 int qsrtb_cholesky_blocked(float* a, int n, int ld, void* workspace, size_t workspace_bytes,

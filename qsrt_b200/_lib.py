@@ -75,6 +75,9 @@ _SIGNATURES = {
     "qsrtb_signed_block_hadamard": (
         _c.c_int, [_PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _PTR]
     ),
+    "qsrtb_mxfp4_signed_block_hadamard": (
+        _c.c_int, [_PTR, _PTR, _c.c_int64, _c.c_int, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR, _c.c_int, _PTR]
+    ),
     "qsrtb_col_sumsq": (
         _c.c_int,
         [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int64, _PTR, _c.c_int64, _PTR,

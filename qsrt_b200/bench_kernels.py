@@ -15,7 +15,7 @@ import json
 
 import torch
 
-from . import allocation, codec, coupled, encoder, hessian, mxfp4, records, refine, storage, tables
+from . import allocation, codec, coupled, encoder, hessian, linalg, mxfp4, records, refine, scoring, storage, tables
 from . import tiles as tile_search
 
 
@@ -126,7 +126,48 @@ def main() -> None:
     rf_states = rf_states.reshape(rf_rows // 16, rf_cols // 16, 256)
     rf_config = refine.H2ViterbiRefineConfig(sweeps=1)
     del rf_x, rf_tiles, rf_recon
+    # tensor-core products and scoring at the headline shapes: 4096 routed rows of one expert
+    sc_rows = args.rows
+    sc_x = linalg.split_tf32(x)                                            # [rows, 7168]
+    sc_gate_up = linalg.split_tf32(torch.randn((4096, k), device=dev, generator=g) * 0.02)   # stacked gate / up
+    sc_down = linalg.split_tf32(torch.randn((k, 2048), device=dev, generator=g) * 0.02)
+    sc_pre = torch.empty((sc_rows, 4096), device=dev)
+    sc_mid, _ = scoring.gated_activation(torch.randn((sc_rows, 4096), device=dev, generator=g))
+    sc_out = torch.empty((sc_rows, k), device=dev)
+    sc_ref = torch.randn((sc_rows, k), device=dev, generator=g)
+    chol_x = torch.randn((k + 512, k), device=dev, generator=g)
+    chol_h = chol_x.T @ chol_x / chol_x.shape[0]
+    chol_h.diagonal().add_(0.025 * chol_h.diagonal().mean())
+    chol_work = torch.empty_like(chol_h)
+    del chol_x
+    chol_copy_ms = _time(lambda: chol_work.copy_(chol_h), args.iters) if not args.only or "cholesky" in args.only else 0.0
+
+    def factor():
+        chol_work.copy_(chol_h)
+        linalg.cholesky_(chol_work)
+
+    syrk_panel = linalg.split_tf32(torch.randn((k - 128, 128), device=dev, generator=g))
+    mx_out = torch.empty((mx_rows, mx_cols), device=dev)
+
+    def fused_ingest():
+        encoder._lib.check(lib.qsrtb_mxfp4_signed_block_hadamard(
+            mx_packed.data_ptr(), mx_scale.data_ptr(), mx_rows, mx_cols, mx_out.data_ptr(), mx_cols, 1, 0, 512,
+            signs_k.data_ptr(), 1, None), "fused ingest")
+
     cases = {
+        f"gemm3x tcgen05 (gate|up pre-activations) [{sc_rows}, {k}] x [4096, {k}]^T":
+            (lambda: linalg.gemm_nt(sc_x, sc_gate_up, sc_pre), 2 * sc_rows * 4096 * k, "F"),
+        f"gemm3x tcgen05 (down product) [{sc_rows}, 2048] x [{k}, 2048]^T":
+            (lambda: linalg.gemm_nt(sc_mid, sc_down, sc_out), 2 * sc_rows * 2048 * k, "F"),
+        f"gemm3x tcgen05 (Cholesky trailing update, rank 128, lower tiles of {k - 128}^2)":
+            (lambda: linalg.gemm_nt(syrk_panel, syrk_panel, h[:k - 128, :k - 128], alpha=-1.0, beta=1.0, lower_only=True),
+             (k - 128) * (k - 128) * 128, "F"),
+        f"cholesky_blocked {k} (copy of {chol_copy_ms:.2f} ms included)": (factor, k * k * k / 3, "F"),
+        "split_tf32 (rows -> head / tail planes)": (lambda: linalg.split_tf32(x, out=sc_x), 12 * sc_rows * k, "B"),
+        "gated_activation (SiLU, -> planes)":
+            (lambda: scoring.gated_activation(sc_pre, "silu"), sc_rows * 4096 * 4 + 2 * sc_rows * 2048 * 4, "B"),
+        "routed_row_sse": (lambda: scoring.row_sse(sc_ref, sc_out, energy=True), 8 * sc_rows * k, "B"),
+        "mxfp4 -> signed_block_hadamard rows 512 (fused ingest)": (fused_ingest, mx_bytes, "B"),
         "refine_h2_viterbi_paths, one sweep [2048, 7168] K3 (128 row blocks of 448 tiles)":
             (lambda: refine.refine_h2_viterbi_paths(rf_weight, rf_hessian, rf_q, rf_states, rf_args, rf_config),
              (rf_rows // 16) * (rf_cols // 16), "T"),

@@ -239,23 +239,50 @@ def ldlq_mixed_batched(
         finally:
             torch.backends.cuda.matmul.allow_tf32 = allow
 
+    # Feedback products on the tensor cores (see encoder._ldlq_steps): the transposed factors are
+    # split once per source, the transposed error rows of the current span after every step.
+    tensor_cores = bool(args0.get("ldlq_tensor_cores", enc.LDLQ_TENSOR_CORES))
+    if tensor_cores:
+        from . import linalg
+
+        factor_t = linalg.split_tf32(Ls, transpose=True)
+        err_t = linalg.Planes(torch.zeros((batch, size_n, buffer_rows), dtype=torch.float, device=device),
+                              torch.zeros((batch, size_n, buffer_rows), dtype=torch.float, device=device))
+
+        def factor_view(rows, cols):
+            return linalg.Planes(pick(factor_t.hi[:, rows, cols]), pick(factor_t.lo[:, rows, cols]))
+
     step = 0
     for end in range(process_end, process_begin, -buffer_rows):
         begin = end - buffer_rows
         for block_end in range(buffer_rows, 0, -16):
             row_begin, row_end = begin + block_end - 16, begin + block_end
             if row_end < end:
-                gemm(product_cache[:, row_begin:row_end],
-                     pick(Ls[:, row_end:end, row_begin:row_end]).transpose(1, 2), err[:, row_end:end])
+                if tensor_cores:
+                    linalg.gemm_nt(linalg.Planes(err_t.hi[:, :, block_end:], err_t.lo[:, :, block_end:]),
+                                   factor_view(slice(row_begin, row_end), slice(row_end, end)),
+                                   product_cache[:, row_begin:row_end], beta=1.0, transposed_out=True)
+                else:
+                    gemm(product_cache[:, row_begin:row_end],
+                         pick(Ls[:, row_end:end, row_begin:row_end]).transpose(1, 2), err[:, row_end:end])
             for launch in launches.at(row_begin // 16):
                 _quantize_members(weights, product_cache, weights_q, err, encoded_q, row_begin, launch, args0)
+            if tensor_cores:
+                linalg.split_tf32(err[:, row_begin:row_end], transpose=True,
+                                  out=linalg.Planes(err_t.hi[:, :, block_end - 16:block_end],
+                                                    err_t.lo[:, :, block_end - 16:block_end]))
             if pb:
                 step += 1
                 pb.update(step)
         if begin:
             # rows at or above `begin` are committed; only the rows still to be visited need the
             # span's error folded into their product cache
-            gemm(product_cache[:, :begin], pick(Ls[:, begin:end, :begin]).transpose(1, 2), err[:, begin:end])
+            if tensor_cores:
+                linalg.gemm_nt(factor_view(slice(0, begin), slice(begin, end)), err_t, product_cache[:, :begin], beta=1.0)
+            else:
+                gemm(product_cache[:, :begin], pick(Ls[:, begin:end, :begin]).transpose(1, 2), err[:, begin:end])
+    if tensor_cores:
+        linalg.check_status(device)
     if synchronize:
         torch.cuda.synchronize(device)
     if return_product_cache:

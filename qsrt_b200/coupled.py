@@ -157,6 +157,60 @@ def encode_coupled_weights(weights: WeightTriplet, spec: CoupledHadamardSpec) ->
     return upstream[:intermediate].contiguous(), upstream[intermediate:].contiguous(), down
 
 
+def encode_coupled_weights_mxfp4(sources, spec: CoupledHadamardSpec, *, round_bf16: bool = True) -> WeightTriplet:
+    """``encode_coupled_weights`` for an expert still in its MXFP4 source storage.
+
+    ``sources`` = ``((w1_packed, w1_scale), (w3_packed, w3_scale), (w2_packed, w2_scale))`` with
+    packed codes ``[out, in / 2]`` and E8M0 scales ``[out, in / 32]`` (qsrt/io/mxfp4.py:1-63).  The
+    dequantiser is fused into the first transform of each matrix (``qsrtb_mxfp4_signed_block_hadamard``):
+    the gate and up rows go straight into the interleaved ``[2 I, Hd]`` stack in residual
+    coordinates, the down rows into post-activation coordinates; the remaining column-axis
+    transforms run in place as in ``encode_coupled_weights``.  With ``round_bf16`` every
+    dequantised value is first rounded to bfloat16, the precision in which the source checkpoint
+    is held.  Bit-identical to dequantising and calling ``encode_coupled_weights``."""
+
+    (p1, s1), (p3, s3), (p2, s2) = sources
+    for packed, scale in sources:
+        if packed.dtype != torch.uint8 or scale.dtype != torch.uint8 or packed.ndim != 2 or scale.ndim != 2:
+            raise TypeError("MXFP4 sources are uint8 matrices of packed codes and block scales")
+        if not packed.is_cuda or scale.device != packed.device:
+            raise ValueError("the B200 coupled transforms require CUDA tensors")
+        if scale.shape != (packed.shape[0], packed.shape[1] * 2 // 32):
+            raise ValueError("scale blocks do not cover the packed codes")
+    intermediate, hidden = p1.shape[0], p1.shape[1] * 2
+    if p3.shape != p1.shape or tuple(p2.shape) != (hidden, intermediate // 2):
+        raise ValueError("coupled weights require matching w1/w3 and w2 [hidden, intermediate]")
+    if hidden % spec.residual_block_size:
+        raise ValueError("hidden size does not close residual Hadamard blocks")
+    if 2 * intermediate % spec.preactivation_block_size:
+        raise ValueError("interleaved size does not close preactivation blocks")
+    if intermediate % spec.postactivation_block_size:
+        raise ValueError("intermediate size does not close postactivation blocks")
+    device = p1.device
+    input_signs = rotation_signs(hidden, draw=spec.residual_draw, axis=0, device=device)
+    pre_signs = rotation_signs(2 * intermediate, draw=spec.intermediate_draw, axis=1, device=device)
+    post_signs = rotation_signs(intermediate, draw=spec.intermediate_draw, axis=2, device=device)
+    output_signs = rotation_signs(hidden, draw=spec.residual_draw, axis=3, device=device)
+
+    def ingest(packed, scale, out, row_step, row_offset, block, signs):
+        packed, scale = packed.contiguous(), scale.contiguous()
+        with torch.cuda.device(device):
+            _lib.check(
+                _lib.lib().qsrtb_mxfp4_signed_block_hadamard(
+                    packed.data_ptr(), scale.data_ptr(), packed.shape[0], packed.shape[1] * 2, out.data_ptr(),
+                    out.stride(0), row_step, row_offset, block, signs.data_ptr(), int(round_bf16), _stream_ptr(device)),
+                "qsrtb_mxfp4_signed_block_hadamard")
+
+    upstream = torch.empty((2 * intermediate, hidden), dtype=torch.float32, device=device)
+    ingest(p1, s1, upstream, 2, 0, spec.residual_block_size, input_signs)
+    ingest(p3, s3, upstream, 2, 1, spec.residual_block_size, input_signs)
+    _transform_(upstream, 0, spec.preactivation_block_size, pre_signs, False)
+    down = torch.empty((hidden, intermediate), dtype=torch.float32, device=device)
+    ingest(p2, s2, down, 1, 0, spec.postactivation_block_size, post_signs)
+    _transform_(down, 0, spec.residual_block_size, output_signs, False)
+    return upstream[:intermediate].contiguous(), upstream[intermediate:].contiguous(), down
+
+
 @dataclass(frozen=True)
 class CoupledHadamardExecution:
     """Calibration and scoring operations for one transformed expert basis (:347-543)."""

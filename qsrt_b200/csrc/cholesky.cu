@@ -1,14 +1,14 @@
 // Blocked Cholesky factorisation of a damped Hessian, entirely on the device.
 //
 // Right-looking over panels of 128 columns.  Per panel j:
-//   chol_diag_kernel : one CTA factors the 128 x 128 diagonal block in shared memory (unblocked,
-//                      float32).  A pivot that is not positive is reported through a device status
+//   chol_diag_kernel : one CTA factors the 128 x 128 diagonal block in shared memory, blocked by 16
+//                      columns (float32).  A pivot that is not positive is reported through a device status
 //                      word (its 1-based column, as LAPACK's `info`) and every later kernel of the
 //                      call turns into a no-op: nothing traps, nothing throws, the host reads the
 //                      word once after the call and runs the retry-with-damping loop of the reference
 //                      (qsrt/exl3_encoder_backend.py:331-370).
 //   chol_panel_kernel: the rows below solve  X * L_jj^T = A  by forward substitution, one row per
-//                      thread with eight columns register-blocked; X goes back into the matrix and,
+//                      thread, 16 columns at a time in registers; X goes back into the matrix and,
 //                      split into its TF32 head and tail, into the two operand planes of the update.
 //   trailing update  : A_22 -= X X^T on the tensor cores (qsrtb_gemm3x_tc: tcgen05 / TMEM, three
 //                      TF32 products per float32 product), lower tiles only.
@@ -23,7 +23,6 @@
 namespace {
 
 constexpr int kPanel = 128;
-constexpr int kRowsPerCta = 64;
 
 __device__ __forceinline__ float tf32_head(float x)
 {
@@ -32,42 +31,115 @@ __device__ __forceinline__ float tf32_head(float x)
     return __uint_as_float(u & 0xffffe000u);
 }
 
-// Factor the w x w block at a[0 .. w)[0 .. w) (pitch ld) in place (lower triangle).
+constexpr int kPitch = kPanel + 1;   // shared-memory tile pitch: conflict-free row and column access
+constexpr int kSub = 16;             // inner block of the diagonal factorisation
+constexpr int kThreads = 256;
+
+// Factor the w x w block at a[0 .. w)[0 .. w) (pitch ld) in place; w is a multiple of 16.
+// Blocked right-looking inside shared memory, 16 columns at a time:
+//   (a) warp 0 factors the 16 x 16 diagonal sub-block, a lane per row, the row in registers, the
+//       column exchanged by shuffles (no block barrier inside);
+//   (b) a thread per remaining row solves its 16 panel entries against that sub-block;
+//   (c) two threads per remaining row subtract the panel's outer product from the row's entries
+//       left of the diagonal (each reads the other rows' panel entries as 16-byte broadcasts).
+// On return the lower triangle holds the factor and the strict upper triangle its transpose
+// (which is how the panel kernel wants to read it).
 // status[0]: 0 or the 1-based global column of the first non-positive pivot.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kThreads)
 chol_diag_kernel(float* __restrict__ a, int w, int ld, int first_column, int* __restrict__ status)
 {
     if (status[0] != 0) return;
-    extern __shared__ float block[];   // [w][kPanel + 1]
-    constexpr int pitch = kPanel + 1;
+    extern __shared__ __align__(16) float smem[];
+    float* tile = smem;                           // [kPanel][kPitch]
+    float* pan = smem + kPanel * kPitch;          // [kPanel][kSub]: current panel, rows below the sub-block
+    float* fac = pan + kPanel * kSub;             // [kSub][kSub + 1]: current factored sub-block
+    __shared__ float fac_inv[kSub];               // reciprocals of its diagonal
     __shared__ int bad;
-    const int t = threadIdx.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     if (t == 0) bad = 0;
-    for (int i = t; i < w * w; i += blockDim.x) {
+    for (int i = t; i < w * w; i += kThreads) {
         const int r = i / w, c = i - r * w;
-        block[r * pitch + c] = (c <= r) ? a[int64_t(r) * ld + c] : 0.0f;
+        tile[r * kPitch + c] = a[int64_t(r) * ld + c];
     }
     __syncthreads();
-    for (int c = 0; c < w; ++c) {
-        if (t == 0) {
-            const float pivot = block[c * pitch + c];
-            if (!(pivot > 0.0f) || !(pivot <= 3.0e38f)) {   // also catches NaN and infinity
-                bad = first_column + c + 1;
-                block[c * pitch + c] = 1.0f;
-            } else {
-                block[c * pitch + c] = sqrtf(pivot);
+    for (int j0 = 0; j0 < w; j0 += kSub) {
+        if (warp == 0) {
+            float row[kSub];
+            float row_inv = 1.0f;   // lane c: reciprocal of the c-th diagonal entry of the factor
+            const int src = lane < kSub ? lane : 0;
+#pragma unroll
+            for (int k = 0; k < kSub; ++k) row[k] = tile[(j0 + src) * kPitch + j0 + k];
+#pragma unroll
+            for (int c = 0; c < kSub; ++c) {
+                const float p = __shfl_sync(0xffffffffu, row[c], c);
+                const bool ok = p > 0.0f && p <= 3.0e38f;   // also rejects NaN and infinity
+                if (!ok && lane == 0 && bad == 0) bad = first_column + j0 + c + 1;
+                // 1 / sqrt(p) once per column (correctly rounded division, then products): the serial
+                // part of the whole factorisation runs through these few instructions
+                const float inv = ok ? 1.0f / sqrtf(p) : 1.0f;
+                const float l = lane > c ? row[c] * inv : (lane == c ? p * inv : 0.0f);
+                if (lane == c) row_inv = inv;
+                row[c] = l;
+#pragma unroll
+                for (int k = c + 1; k < kSub; ++k) {
+                    const float lk = __shfl_sync(0xffffffffu, l, k);
+                    if (lane >= k) row[k] = fmaf(-l, lk, row[k]);
+                }
+            }
+            if (lane < kSub) {
+#pragma unroll
+                for (int k = 0; k < kSub; ++k) {
+                    fac[lane * (kSub + 1) + k] = row[k];
+                    if (k <= lane) tile[(j0 + lane) * kPitch + j0 + k] = row[k];
+                }
+                fac_inv[lane] = row_inv;
             }
         }
         __syncthreads();
         if (bad != 0) break;
-        const float diag = block[c * pitch + c];
-        for (int r = c + 1 + t; r < w; r += blockDim.x) block[r * pitch + c] = block[r * pitch + c] / diag;
+        const int below = w - j0 - kSub;   // rows under the sub-block
+        if (t < below) {
+            const int r = j0 + kSub + t;
+            float x[kSub];
+#pragma unroll
+            for (int k = 0; k < kSub; ++k) x[k] = tile[r * kPitch + j0 + k];
+            // column by column, so that the updates of one column are independent of each other
+#pragma unroll
+            for (int c = 0; c < kSub; ++c) {
+                x[c] *= fac_inv[c];
+#pragma unroll
+                for (int k = c + 1; k < kSub; ++k) x[k] = fmaf(-x[c], fac[k * (kSub + 1) + c], x[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < kSub; ++k) {
+                tile[r * kPitch + j0 + k] = x[k];
+                pan[t * kSub + k] = x[k];
+            }
+        }
         __syncthreads();
-        // rank-1 update of the trailing lower triangle: element (r, k), c < k <= r < w
-        for (int r = c + 1 + (t >> 4); r < w; r += 16) {
-            const float lr = block[r * pitch + c];
-            for (int k = c + 1 + (t & 15); k <= r; k += 16)
-                block[r * pitch + k] = fmaf(-lr, block[k * pitch + c], block[r * pitch + k]);
+        {
+            const int rr = t >> 1, half = t & 1;
+            if (rr < below) {
+                float mine[kSub];
+#pragma unroll
+                for (int q = 0; q < kSub / 4; ++q) {
+                    const float4 v = *reinterpret_cast<const float4*>(pan + rr * kSub + 4 * q);
+                    mine[4 * q] = v.x; mine[4 * q + 1] = v.y; mine[4 * q + 2] = v.z; mine[4 * q + 3] = v.w;
+                }
+                float* row = tile + (j0 + kSub + rr) * kPitch + j0 + kSub;
+                for (int k = half; k <= rr; k += 2) {
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < kSub / 4; ++q) {
+                        const float4 v = *reinterpret_cast<const float4*>(pan + k * kSub + 4 * q);
+                        s0 = fmaf(mine[4 * q], v.x, s0);
+                        s1 = fmaf(mine[4 * q + 1], v.y, s1);
+                        s2 = fmaf(mine[4 * q + 2], v.z, s2);
+                        s3 = fmaf(mine[4 * q + 3], v.w, s3);
+                    }
+                    row[k] -= (s0 + s1) + (s2 + s3);
+                }
+            }
         }
         __syncthreads();
     }
@@ -75,72 +147,78 @@ chol_diag_kernel(float* __restrict__ a, int w, int ld, int first_column, int* __
         if (t == 0) atomicCAS(status, 0, bad);
         return;
     }
-    // lower triangle: the factor; strict upper triangle: its transpose, which is how the panel
-    // kernel wants to read it (row k holds L[k..w)[k], contiguous)
-    for (int i = t; i < w * w; i += blockDim.x) {
+    for (int i = t; i < w * w; i += kThreads) {
         const int r = i / w, c = i - r * w;
-        a[int64_t(r) * ld + c] = (c <= r) ? block[r * pitch + c] : block[c * pitch + r];
+        a[int64_t(r) * ld + c] = (c <= r) ? tile[r * kPitch + c] : tile[c * kPitch + r];
     }
 }
 
-// X = A * L^-T for kRowsPerCta rows below a factored kPanel x kPanel diagonal block.
+// X = A * L^-T for the rows below a factored kPanel x kPanel diagonal block: one row per thread
+// (threads 0 .. 127; all 256 threads stage the operands), forward substitution in chunks of 16
+// columns held in registers against the transposed factor in shared memory (every thread reads the
+// same factor addresses: broadcasts).
 //   diag  : the factored diagonal block (lower triangle and its transpose above it, pitch ld)
 //   below : first row below it (same columns, pitch ld), `rows` rows
 //   hi/lo : [rows, kPanel] planes receiving the TF32 head and tail of X
-__global__ void __launch_bounds__(kRowsPerCta)
+__global__ void __launch_bounds__(kThreads)
 chol_panel_kernel(const float* __restrict__ diag, float* __restrict__ below, int rows, int ld,
                   float* __restrict__ hi, float* __restrict__ lo, const int* __restrict__ status)
 {
     if (status[0] != 0) return;
-    extern __shared__ float smem[];
-    float* lt = smem;                          // lt[t * kPanel + c] = L[c][t]  (t <= c)
-    float* x = smem + kPanel * kPanel;         // x[r * (kPanel + 1) + c]
-    constexpr int xp = kPanel + 1;
+    extern __shared__ __align__(16) float smem[];
+    float* lt = smem;                          // lt[k * kPanel + c] = L[c][k]  (k <= c)
+    float* tile = smem + kPanel * kPanel;      // [kPanel][kPitch]
     const int t = threadIdx.x;
-    const int row0 = blockIdx.x * kRowsPerCta;
-    const int count = min(kRowsPerCta, rows - row0);
-    for (int i = t; i < kPanel * kPanel; i += kRowsPerCta) {
-        const int k = i / kPanel, c = i - k * kPanel;   // entries with c < k are never read
-        lt[i] = diag[int64_t(k) * ld + c];
+    const int row0 = blockIdx.x * kPanel;
+    const int count = min(kPanel, rows - row0);
+    for (int i = t; i < kPanel * kPanel / 4; i += kThreads) {
+        const int k = i / (kPanel / 4), c4 = i - k * (kPanel / 4);   // entries left of the diagonal are never read
+        reinterpret_cast<float4*>(lt)[i] = *reinterpret_cast<const float4*>(diag + int64_t(k) * ld + 4 * c4);
     }
-    for (int i = t; i < count * kPanel; i += kRowsPerCta) {
-        const int r = i / kPanel, c = i - r * kPanel;
-        x[r * xp + c] = below[int64_t(row0 + r) * ld + c];
+    for (int i = t; i < count * (kPanel / 4); i += kThreads) {
+        const int r = i / (kPanel / 4), c = (i - r * (kPanel / 4)) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(below + int64_t(row0 + r) * ld + c);
+        float* dst = tile + r * kPitch + c;
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
     }
     __syncthreads();
     if (t < count) {
-        float* mine = x + t * xp;
-        for (int c0 = 0; c0 < kPanel; c0 += 8) {
-            float acc[8];
+        float* mine = tile + t * kPitch;
+        for (int c0 = 0; c0 < kPanel; c0 += kSub) {
+            float acc[kSub];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = mine[c0 + i];
+            for (int i = 0; i < kSub; ++i) acc[i] = mine[c0 + i];
+#pragma unroll 2
             for (int k = 0; k < c0; ++k) {
                 const float xv = mine[k];
-                const float4 l0 = *reinterpret_cast<const float4*>(lt + k * kPanel + c0);
-                const float4 l1 = *reinterpret_cast<const float4*>(lt + k * kPanel + c0 + 4);
-                acc[0] = fmaf(-xv, l0.x, acc[0]); acc[1] = fmaf(-xv, l0.y, acc[1]);
-                acc[2] = fmaf(-xv, l0.z, acc[2]); acc[3] = fmaf(-xv, l0.w, acc[3]);
-                acc[4] = fmaf(-xv, l1.x, acc[4]); acc[5] = fmaf(-xv, l1.y, acc[5]);
-                acc[6] = fmaf(-xv, l1.z, acc[6]); acc[7] = fmaf(-xv, l1.w, acc[7]);
+#pragma unroll
+                for (int q = 0; q < kSub / 4; ++q) {
+                    const float4 l = *reinterpret_cast<const float4*>(lt + k * kPanel + c0 + 4 * q);
+                    acc[4 * q] = fmaf(-xv, l.x, acc[4 * q]);
+                    acc[4 * q + 1] = fmaf(-xv, l.y, acc[4 * q + 1]);
+                    acc[4 * q + 2] = fmaf(-xv, l.z, acc[4 * q + 2]);
+                    acc[4 * q + 3] = fmaf(-xv, l.w, acc[4 * q + 3]);
+                }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float s = acc[i];
+            for (int i = 0; i < kSub; ++i) {
+                acc[i] = acc[i] / lt[(c0 + i) * kPanel + c0 + i];
 #pragma unroll
-                for (int k = 0; k < i; ++k) s = fmaf(-acc[k], lt[(c0 + k) * kPanel + c0 + i], s);
-                acc[i] = s / lt[(c0 + i) * kPanel + c0 + i];
+                for (int k = i + 1; k < kSub; ++k) acc[k] = fmaf(-acc[i], lt[(c0 + i) * kPanel + c0 + k], acc[k]);
                 mine[c0 + i] = acc[i];
             }
         }
     }
     __syncthreads();
-    for (int i = t; i < count * kPanel; i += kRowsPerCta) {
-        const int r = i / kPanel, c = i - r * kPanel;
-        const float v = x[r * xp + c];
-        const float head = tf32_head(v);
-        below[int64_t(row0 + r) * ld + c] = v;
-        hi[int64_t(row0 + r) * kPanel + c] = head;
-        lo[int64_t(row0 + r) * kPanel + c] = tf32_head(v - head);
+    for (int i = t; i < count * (kPanel / 4); i += kThreads) {
+        const int r = i / (kPanel / 4), c = (i - r * (kPanel / 4)) * 4;
+        const float* src = tile + r * kPitch + c;
+        const float4 v = make_float4(src[0], src[1], src[2], src[3]);
+        const float4 head = make_float4(tf32_head(v.x), tf32_head(v.y), tf32_head(v.z), tf32_head(v.w));
+        *reinterpret_cast<float4*>(below + int64_t(row0 + r) * ld + c) = v;
+        *reinterpret_cast<float4*>(hi + int64_t(row0 + r) * kPanel + c) = head;
+        *reinterpret_cast<float4*>(lo + int64_t(row0 + r) * kPanel + c) =
+            make_float4(tf32_head(v.x - head.x), tf32_head(v.y - head.y), tf32_head(v.z - head.z), tf32_head(v.w - head.w));
     }
 }
 
@@ -157,7 +235,8 @@ extern "C" int qsrtb_cholesky_workspace_bytes(int n, size_t* bytes)
 extern "C" int qsrtb_cholesky_blocked(float* a, int n, int ld, void* workspace, size_t workspace_bytes,
                                       int* status, void* stream)
 {
-    if (!a || n < 0 || ld < n) return qsrtb_fail(QSRTB_EINVAL, "bad matrix arguments");
+    if (!a || n < 0 || ld < n || (n % 16) != 0)
+        return qsrtb_fail(QSRTB_EINVAL, "the matrix size must be a multiple of 16 (the block size of the block-LDL factor)");
     if ((ld % 4) != 0 || (reinterpret_cast<uintptr_t>(a) & 15))
         return qsrtb_fail(QSRTB_EINVAL, "matrix rows must be 16-byte aligned");
     if (!status) return qsrtb_fail(QSRTB_EINVAL, "status pointer required");
@@ -170,8 +249,8 @@ extern "C" int qsrtb_cholesky_blocked(float* a, int n, int ld, void* workspace, 
     float* hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
     float* lo = hi + (n > kPanel ? size_t(n - kPanel) * kPanel : 0);
 
-    const int diag_smem = kPanel * (kPanel + 1) * int(sizeof(float));
-    const int panel_smem = (kPanel * kPanel + kRowsPerCta * (kPanel + 1)) * int(sizeof(float));
+    const int diag_smem = (kPanel * kPitch + kPanel * kSub + kSub * (kSub + 1)) * int(sizeof(float));
+    const int panel_smem = (kPanel * kPanel + kPanel * kPitch) * int(sizeof(float));
     cudaError_t err = cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, diag_smem);
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "cudaFuncSetAttribute(chol_diag)");
     err = cudaFuncSetAttribute(chol_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, panel_smem);
@@ -180,12 +259,12 @@ extern "C" int qsrtb_cholesky_blocked(float* a, int n, int ld, void* workspace, 
     for (int j = 0; j < n; j += kPanel) {
         const int w = n - j < kPanel ? n - j : kPanel;
         float* block = a + int64_t(j) * ld + j;
-        chol_diag_kernel<<<1, 256, diag_smem, s>>>(block, w, ld, j, status);
+        chol_diag_kernel<<<1, kThreads, diag_smem, s>>>(block, w, ld, j, status);
         const int rows = n - j - w;
         if (rows <= 0) break;
         // w == kPanel here: only the last panel can be narrower, and it has no rows below
         float* below = a + int64_t(j + w) * ld + j;
-        chol_panel_kernel<<<(rows + kRowsPerCta - 1) / kRowsPerCta, kRowsPerCta, panel_smem, s>>>(
+        chol_panel_kernel<<<(rows + kPanel - 1) / kPanel, kThreads, panel_smem, s>>>(
             block, below, rows, ld, hi, lo, status);
         err = cudaGetLastError();
         if (err != cudaSuccess) return qsrtb_fail_cuda(err, "Cholesky panel launch");

@@ -19,29 +19,11 @@
 
 namespace {
 
+// Unnormalised Walsh-Hadamard of one block of 128 * SEGS values held by a warp: lane l owns
+// values 4l .. 4l+3 of every 128-value segment.
 template <int SEGS>
-__global__ void __launch_bounds__(256)
-signed_hadamard_rows_kernel(float* __restrict__ x, int64_t rows, int cols, int ld,
-                            const float* __restrict__ signs, int sign_after, float norm)
+__device__ __forceinline__ void butterflies(float (&v)[SEGS][4], const int lane)
 {
-    constexpr int BLOCK = 128 * SEGS;
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int blocks_per_row = cols / BLOCK;
-    if (warp >= rows * blocks_per_row) return;
-    const int64_t r = warp / blocks_per_row;
-    const int c0 = int(warp - r * blocks_per_row) * BLOCK;
-    float* base = x + r * ld + c0;
-    float v[SEGS][4];
-#pragma unroll
-    for (int s = 0; s < SEGS; ++s) {
-        const float4 t = *reinterpret_cast<const float4*>(base + s * 128 + lane * 4);
-        v[s][0] = t.x; v[s][1] = t.y; v[s][2] = t.z; v[s][3] = t.w;
-        if (signs && !sign_after) {
-            const float4 g = *reinterpret_cast<const float4*>(signs + c0 + s * 128 + lane * 4);
-            v[s][0] *= g.x; v[s][1] *= g.y; v[s][2] *= g.z; v[s][3] *= g.w;
-        }
-    }
 #pragma unroll
     for (int s = 0; s < SEGS; ++s) {
         // widths 1 and 2: inside the lane's four consecutive values
@@ -73,6 +55,32 @@ signed_hadamard_rows_kernel(float* __restrict__ x, int64_t rows, int cols, int l
             }
         }
     }
+}
+
+template <int SEGS>
+__global__ void __launch_bounds__(256)
+signed_hadamard_rows_kernel(float* __restrict__ x, int64_t rows, int cols, int ld,
+                            const float* __restrict__ signs, int sign_after, float norm)
+{
+    constexpr int BLOCK = 128 * SEGS;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int blocks_per_row = cols / BLOCK;
+    if (warp >= rows * blocks_per_row) return;
+    const int64_t r = warp / blocks_per_row;
+    const int c0 = int(warp - r * blocks_per_row) * BLOCK;
+    float* base = x + r * ld + c0;
+    float v[SEGS][4];
+#pragma unroll
+    for (int s = 0; s < SEGS; ++s) {
+        const float4 t = *reinterpret_cast<const float4*>(base + s * 128 + lane * 4);
+        v[s][0] = t.x; v[s][1] = t.y; v[s][2] = t.z; v[s][3] = t.w;
+        if (signs && !sign_after) {
+            const float4 g = *reinterpret_cast<const float4*>(signs + c0 + s * 128 + lane * 4);
+            v[s][0] *= g.x; v[s][1] *= g.y; v[s][2] *= g.z; v[s][3] *= g.w;
+        }
+    }
+    butterflies<SEGS>(v, lane);
 #pragma unroll
     for (int s = 0; s < SEGS; ++s) {
 #pragma unroll
@@ -83,6 +91,61 @@ signed_hadamard_rows_kernel(float* __restrict__ x, int64_t rows, int cols, int l
         }
         *reinterpret_cast<float4*>(base + s * 128 + lane * 4) = make_float4(v[s][0], v[s][1], v[s][2], v[s][3]);
     }
+}
+
+
+// The same transform along the input axis, reading the source matrix in its packed MXFP4 storage
+// (E2M1 codes, two per byte, low nibble first; one E8M0 scale byte per 32 inputs;
+// qsrt/io/mxfp4.py:1-63) instead of a float32 copy of it: 0.53 bytes per weight come in, the
+// transformed float32 row goes out, and the dequantised matrix never exists in memory.
+// Source row r lands in output row r * row_step + row_offset, which interleaves the gate and up
+// matrices as the coupled coordinates want them (qsrt/qsrt_coupled.py:145-196).
+__device__ __forceinline__ float e2m1_times_scale(uint32_t code, float scale, int round_bf16)
+{
+    const uint32_t m = code & 7u;
+    const float mag = m < 2u ? 0.5f * float(m) : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+    float v = ((code & 8u) ? -mag : mag) * scale;
+    if (round_bf16) {   // round to nearest even on 8 significand bits, as a bfloat16 checkpoint stores it
+        uint32_t u = __float_as_uint(v);
+        if ((u & 0x7f800000u) != 0x7f800000u) u += 0x00007fffu + ((u >> 16) & 1u);
+        v = __uint_as_float(u & 0xffff0000u);
+    }
+    return v;
+}
+
+template <int SEGS>
+__global__ void __launch_bounds__(256)
+mxfp4_signed_hadamard_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
+                                  int64_t rows, int cols, float* __restrict__ out, int ld, int row_step,
+                                  int row_offset, const float* __restrict__ signs, int round_bf16, float norm)
+{
+    constexpr int BLOCK = 128 * SEGS;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int blocks_per_row = cols / BLOCK;
+    if (warp >= rows * blocks_per_row) return;
+    const int64_t r = warp / blocks_per_row;
+    const int c0 = int(warp - r * blocks_per_row) * BLOCK;
+    float v[SEGS][4];
+#pragma unroll
+    for (int s = 0; s < SEGS; ++s) {
+        const int c = c0 + s * 128 + lane * 4;
+        const uint32_t codes = *reinterpret_cast<const uint16_t*>(packed + r * (cols / 2) + c / 2);
+        const uint32_t byte = scale[r * (cols / 32) + c / 32];
+        const float sc = __uint_as_float(byte == 0u ? 0x00400000u : byte << 23);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[s][i] = e2m1_times_scale((codes >> (4 * i)) & 15u, sc, round_bf16);
+        if (signs) {
+            const float4 g = *reinterpret_cast<const float4*>(signs + c);
+            v[s][0] *= g.x; v[s][1] *= g.y; v[s][2] *= g.z; v[s][3] *= g.w;
+        }
+    }
+    butterflies<SEGS>(v, lane);
+    float* base = out + (r * row_step + row_offset) * ld + c0;
+#pragma unroll
+    for (int s = 0; s < SEGS; ++s)
+        *reinterpret_cast<float4*>(base + s * 128 + lane * 4) =
+            make_float4(__fdiv_rn(v[s][0], norm), __fdiv_rn(v[s][1], norm), __fdiv_rn(v[s][2], norm), __fdiv_rn(v[s][3], norm));
 }
 
 // 128-row strips; `finish` applies the division and the trailing signs (single-pass blocks).
@@ -198,5 +261,34 @@ extern "C" int qsrtb_signed_block_hadamard(float* x, int64_t rows, int cols, int
     }
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return qsrtb_fail_cuda(err, "signed_block_hadamard launch");
+    return QSRTB_OK;
+}
+
+extern "C" int qsrtb_mxfp4_signed_block_hadamard(const uint8_t* packed, const uint8_t* scale, int64_t rows, int cols,
+                                                 float* out, int ld, int row_step, int row_offset, int block_size,
+                                                 const float* signs, int round_bf16, void* stream)
+{
+    if (rows < 0 || cols < 0 || ld < cols || (ld % 4) != 0 || row_step < 1 || row_offset < 0 || row_offset >= row_step)
+        return qsrtb_fail(QSRTB_EINVAL, "bad matrix arguments");
+    if (block_size != 128 && block_size != 256 && block_size != 512)
+        return qsrtb_fail(QSRTB_EINVAL, "block_size must be 128, 256 or 512");
+    if (cols % block_size) return qsrtb_fail(QSRTB_EINVAL, "Hadamard axis must be divisible by block_size");
+    if (rows == 0 || cols == 0) return QSRTB_OK;
+    if (!packed || !scale || !out) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
+    if ((reinterpret_cast<uintptr_t>(packed) & 1) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+        (signs && (reinterpret_cast<uintptr_t>(signs) & 15)))
+        return qsrtb_fail(QSRTB_EINVAL, "packed codes need 2-byte, output and signs 16-byte alignment");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float norm = sqrtf(float(block_size));
+    const int64_t warps = rows * (cols / block_size);
+    const unsigned blocks = unsigned((warps + 7) / 8);
+    if (block_size == 128)
+        mxfp4_signed_hadamard_rows_kernel<1><<<blocks, 256, 0, s>>>(packed, scale, rows, cols, out, ld, row_step, row_offset, signs, round_bf16, norm);
+    else if (block_size == 256)
+        mxfp4_signed_hadamard_rows_kernel<2><<<blocks, 256, 0, s>>>(packed, scale, rows, cols, out, ld, row_step, row_offset, signs, round_bf16, norm);
+    else
+        mxfp4_signed_hadamard_rows_kernel<4><<<blocks, 256, 0, s>>>(packed, scale, rows, cols, out, ld, row_step, row_offset, signs, round_bf16, norm);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return qsrtb_fail_cuda(err, "mxfp4_signed_block_hadamard launch");
     return QSRTB_OK;
 }

@@ -44,11 +44,12 @@ SIGMA_REG = 0.025
 # this to False to reproduce the reference's placement exactly.
 KEEP_HESSIAN_ON_DEVICE = True
 
-# Feedback products of the BlockLDLQ recursion: False = the float32 library GEMMs the reference
-# itself calls (same rounding as the reference up to summation order), True = this library's
-# tensor-core products (float32 accuracy from three TF32 products).  ``quant_args["ldlq_tensor_cores"]``
-# overrides it per call.
-LDLQ_TENSOR_CORES = False
+# Feedback products of the BlockLDLQ recursion: True = this library's tensor-core products
+# (tcgen05, float32 accuracy from three TF32 products; the result of a product does not depend on
+# how matrices are batched, so stacked and one-by-one encodes agree bit for bit), False = the
+# float32 library GEMMs the reference itself calls.  ``quant_args["ldlq_tensor_cores"]`` overrides
+# it per call.
+LDLQ_TENSOR_CORES = True
 
 finalize_capture_H_mutex = threading.Lock()
 _SHARED_INPUT_SCALES: dict = {}
@@ -461,11 +462,70 @@ def relocate_g_scale_to_sv(su: torch.Tensor, sv: torch.Tensor, g_scale: float):
     return su * g_scale, sv / g_scale
 
 
+def prime_shared_input_scales(weight: torch.Tensor, quant_args: dict, H_diag: torch.Tensor | None = None) -> torch.Tensor:
+    """Seed the shared input-scale profile of ``quant_args["shared_input_scales_key"]`` from
+    ``weight`` ([in, out], left untouched) and return it.
+
+    In shared-su mode the first tensor encoded with a key defines the per-input-channel scale
+    profile of every later tensor with that key (exl3_encoder_backend.py:2664-2672); in a canonical
+    full-layer encode that tensor is expert zero's.  A worker that holds only a shard of the
+    experts obtains the same profile by running expert zero's matrices through this function
+    before its first encode.  The reference's split workers repeat expert zero's whole encode for
+    that and discard the payload (scripts/pack_qsrt_candidates.py:1413-1425); the profile only
+    depends on the first half of ``regularize``, which is all that runs here."""
+
+    key = quant_args.get("shared_input_scales_key")
+    if key is None:
+        raise ValueError("quant_args carries no shared_input_scales_key")
+    work = weight.to(torch.float32).contiguous().clone()
+    scratch_args = dict(quant_args)
+    su = torch.ones((work.shape[0], 1), dtype=torch.float32, device=work.device)
+    sv = output_signs(work.shape[1], work.device, scratch_args)
+    _regularize_head(work, su, sv, scratch_args, False, H_diag, False)
+    return _SHARED_INPUT_SCALES[key]
+
+
+def clear_shared_input_scales() -> None:
+    """Forget every shared input-scale profile (between layers, or between tests)."""
+
+    _SHARED_INPUT_SCALES.clear()
+
+
 def regularize(weight: torch.Tensor, su: torch.Tensor, sv: torch.Tensor, quant_args: dict, verbose: bool,
                H_diag: torch.Tensor | None, pb, skip_g_scale: bool = False, q_fallback: bool = False):
     """Sign flips, channel scales, both Hadamards and the global scale
     (exl3_encoder_backend.py:2580-2708).  ``weight`` [in, out] is transformed in place by two
     fused kernels (divide-by-sv + output Hadamard + row sums; divide-by-su + input Hadamard)."""
+
+    apply_out_scales, su, sv = _regularize_head(weight, su, sv, quant_args, verbose, H_diag, q_fallback)
+
+    # weight /= su ; input Hadamard
+    _hadamard(weight, 0, su.reshape(-1).contiguous(), per_col=False, divide=True)
+
+    if not skip_g_scale:
+        override = quant_args.get("g_scale_override")
+        if override is None:
+            g_scale, mse_scale = g_scale_gss(weight, False, quant_args, pb=pb)
+        else:
+            if isinstance(override, bool) or not isinstance(override, (int, float)):
+                raise TypeError("g_scale_override must be a real number")
+            g_scale = float(override)
+            if not math.isfinite(g_scale) or g_scale <= 0.0:
+                raise ValueError("g_scale_override must be positive and finite")
+            mse_scale = torch.tensor(float("nan"), device=weight.device)
+    else:
+        g_scale = 1.0
+    weight, su, sv = apply_g_scale(weight, su, sv, g_scale, into_sv=bool(quant_args.get("g_scale_into_sv")))
+    if verbose:
+        print(f"     - su/sv std: {su.std().item():.6f}   {sv.std().item():.6f}")
+        print(f"     - global scale: {g_scale:.6f}")
+        print(f"     - apply_out_scales: {str(apply_out_scales)}")
+    return apply_out_scales, weight, g_scale, su, sv
+
+
+def _regularize_head(weight, su, sv, quant_args, verbose, H_diag, q_fallback):
+    """First half of ``regularize``: output scales and signs, output Hadamard, input-channel scale
+    profile (shared or own) folded into ``su``.  Returns ``(apply_out_scales, su, sv)``."""
 
     force_out_scales = quant_args["apply_out_scales"]
     if not q_fallback and H_diag is not None:
@@ -510,29 +570,7 @@ def regularize(weight: torch.Tensor, su: torch.Tensor, sv: torch.Tensor, quant_a
     if shared_key is not None:
         in_channel_scales = _SHARED_INPUT_SCALES.setdefault(shared_key, in_channel_scales)
     su = (su * in_channel_scales / (-codebook_scale) + 1e-10).float()
-
-    # weight /= su ; input Hadamard
-    _hadamard(weight, 0, su.reshape(-1).contiguous(), per_col=False, divide=True)
-
-    if not skip_g_scale:
-        override = quant_args.get("g_scale_override")
-        if override is None:
-            g_scale, mse_scale = g_scale_gss(weight, False, quant_args, pb=pb)
-        else:
-            if isinstance(override, bool) or not isinstance(override, (int, float)):
-                raise TypeError("g_scale_override must be a real number")
-            g_scale = float(override)
-            if not math.isfinite(g_scale) or g_scale <= 0.0:
-                raise ValueError("g_scale_override must be positive and finite")
-            mse_scale = torch.tensor(float("nan"), device=weight.device)
-    else:
-        g_scale = 1.0
-    weight, su, sv = apply_g_scale(weight, su, sv, g_scale, into_sv=bool(quant_args.get("g_scale_into_sv")))
-    if verbose:
-        print(f"     - su/sv std: {su.std().item():.6f}   {sv.std().item():.6f}")
-        print(f"     - global scale: {g_scale:.6f}")
-        print(f"     - apply_out_scales: {str(apply_out_scales)}")
-    return apply_out_scales, weight, g_scale, su, sv
+    return apply_out_scales, su, sv
 
 
 # --------------------------------------------------------------------------------------
@@ -681,9 +719,9 @@ def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan,
     if tensor_cores:
         # Operands of the feedback products, both stored with the contraction index (a row of the
         # current span) contiguous: the transposed factor, split once, and the transposed error
-        # rows of the span, split after every 16-row step.  Rows of the span that are not encoded
-        # yet meet zeros of the factor (it is block-lower with empty diagonal blocks), so stale
-        # finite values in the error planes are harmless; the planes start at zero for that reason.
+        # rows of the span, split after every 16-row step.  A product only ever contracts over rows
+        # that are already encoded, so neither the diagonal blocks of the factor nor error rows
+        # left over from the previous span are read.
         factor_t = _linalg.split_tf32(Ls, transpose=True)                       # [B, column, row]
         err_t = _linalg.Planes(torch.zeros((batch, size_n, buf_size_k), dtype=torch.float, device=device),
                                torch.zeros((batch, size_n, buf_size_k), dtype=torch.float, device=device))
@@ -707,7 +745,8 @@ def _ldlq_steps(weights: torch.Tensor, Ls: torch.Tensor, quant_args: dict, plan,
             if bj < buf_size_k:
                 # compensation from the rows already encoded inside this span
                 if tensor_cores:
-                    _linalg.gemm_nt(err_t, view(factor_t, slice(i + bi, i + bj), slice(i, j)), comp,
+                    _linalg.gemm_nt(view(err_t, slice(None), slice(bj, buf_size_k)),
+                                    view(factor_t, slice(i + bi, i + bj), slice(i + bj, j)), comp,
                                     beta=1.0, transposed_out=True)
                 else:
                     gemm(comp, Ls[:, i + bj:j, i + bi:i + bj].transpose(1, 2), err[:, i + bj:j])
@@ -909,6 +948,7 @@ _OUT_OF_SCOPE_ARGS = {
     "periodic_rate_schedules": "periodic (within-tile variable) rates",
     "mcg": "the procedural MCG codebook",
     "mul1": "the procedural MUL1 codebook",
+    "return_trellis_diagnostics": "the on-GPU trellis diagnostics accumulator (qsrt/sqg_quantizer.py:90-139)",
 }
 
 

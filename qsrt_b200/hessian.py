@@ -23,7 +23,7 @@ from .tiles import _stream_ptr
 TENSOR_CORE_CHUNK_ROWS = 2048
 # Default for ``weighted_covariance(tensor_cores=None)``.
 USE_TENSOR_CORES = True
-_tc_workspace: dict[str, torch.Tensor] = {}
+_tc_workspace: dict[tuple[str, int], torch.Tensor] = {}   # per device and stream: launches on different streams must not share planes
 _tc_built: list[bool] = []
 
 
@@ -70,7 +70,7 @@ def accumulate_hessian_tensor_cores(lower: torch.Tensor, rows: torch.Tensor, wei
     wanted = ctypes.c_size_t(0)
     _lib.check(_lib.lib().qsrtb_hessian_tc_workspace_bytes(TENSOR_CORE_CHUNK_ROWS, d, ctypes.byref(wanted)),
                "qsrtb_hessian_tc_workspace_bytes")
-    key = str(device)
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
     work = _tc_workspace.get(key)
     if work is None or work.numel() < wanted.value:
         work = torch.empty(wanted.value, dtype=torch.uint8, device=device)
@@ -145,7 +145,8 @@ def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: to
 
     ``chunk_rows`` only bounds the staging copy of host-resident rows; the kernel streams any
     number of rows in one launch.  ``tensor_cores``: ``None`` follows ``USE_TENSOR_CORES``,
-    ``False`` forces the float32 FMA kernel, ``True`` insists on the tensor-core kernel.
+    ``False`` forces the float32 FMA kernel, ``True`` insists on the tensor-core kernel (and raises
+    when the feature count is not a multiple of 128).
     """
 
     if rows.ndim != 2 or weights.ndim != 1 or rows.shape[0] != weights.shape[0]:
@@ -170,7 +171,9 @@ def weighted_covariance(rows: torch.Tensor, weights: torch.Tensor, *, device: to
     if tensor_cores is None:
         use_tc = USE_TENSOR_CORES and dimension % 128 == 0 and tensor_cores_available()
     else:
-        use_tc = bool(tensor_cores) and dimension % 128 == 0
+        use_tc = bool(tensor_cores)
+        if use_tc and dimension % 128:
+            raise ValueError("tensor_cores=True needs a feature count that is a multiple of 128")
     for begin in range(0, int(rows.shape[0]), chunk_rows):
         step = accumulate_hessian_tensor_cores if use_tc else accumulate_hessian
         step(accumulator, rows[begin:begin + chunk_rows], weights[begin:begin + chunk_rows], accumulate=not first)
@@ -344,3 +347,116 @@ def build_expert_hessians(inputs: torch.Tensor, gates: torch.Tensor, source_midd
             "h2_identity_scale": identity_scale,
         }
     return h13, h2, {"gate_square_sum": h13_weight, "h13_local_alpha": float(h13_alpha), **evidence}
+
+
+# --------------------------------------------------------------------------------------
+# capture -> Hessian streaming reducer
+# --------------------------------------------------------------------------------------
+
+def request_step_mask(observations: torch.Tensor, *, request_step_min: int, request_step_max: int | None,
+                      request_steps: list[int] | None) -> torch.Tensor:
+    """Request-epoch mask of captured observations: the epoch is ``observation_id >> 32``
+    (qsrt/capture.py:734-750)."""
+
+    steps = torch.bitwise_right_shift(observations.to(torch.int64), 32)
+    selected = steps >= request_step_min
+    if request_step_max is not None:
+        selected &= steps <= request_step_max
+    if request_steps is not None:
+        selected &= torch.isin(steps, torch.tensor(request_steps, dtype=steps.dtype, device=steps.device))
+    return selected
+
+
+class StreamingHessianReducer:
+    """All requested per-layer ``H13`` matrices in one pass over a capture's sample parts.
+
+    The arithmetic of ``_build_h13_identity_h2_streaming`` (qsrt/capture.py:753-908) without its
+    file handling: the caller reads each sample part (layer ids, split labels, observation ids,
+    gate-square weights, input rows) however it stores them and hands the tensors to ``add_part``;
+    rows are selected per layer by split and request epoch, moved to the device and accumulated
+    into that layer's ``sum_r w_r x_r x_r^T`` by the Hessian kernels of this library (tensor
+    cores when the input size is a multiple of 128).  ``finish`` divides by the weight sums,
+    symmetrises and returns the matrices with the per-layer evidence the reference writes into its
+    manifest (``w13_rows``, ``w13_total_rows``, ``w13_validation_rows``, ``w13_weight_sum``).
+    The ``H2`` prior of this flow is the identity and is built nowhere, as in the reference."""
+
+    SPLITS = {"train": 0, "validation": 1, "all": None}
+
+    def __init__(self, input_size: int, selected: list[int], *, device: torch.device, sample_split: str = "train",
+                 request_step_min: int = 0, request_step_max: int | None = None,
+                 request_steps: list[int] | None = None, tensor_cores: bool | None = None) -> None:
+        if sample_split not in self.SPLITS:
+            raise ValueError("sample_split must be 'train', 'validation' or 'all'")
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError("the B200 Hessian path requires a CUDA device")
+        self.input_size, self.selected, self.device = int(input_size), list(selected), device
+        self.split_value = self.SPLITS[sample_split]
+        self.sample_split = sample_split
+        self.request = dict(request_step_min=request_step_min, request_step_max=request_step_max,
+                            request_steps=request_steps)
+        if tensor_cores is None:
+            tensor_cores = USE_TENSOR_CORES and self.input_size % 128 == 0 and tensor_cores_available()
+        elif tensor_cores and self.input_size % 128:
+            raise ValueError("tensor_cores=True needs an input size that is a multiple of 128")
+        self._step = accumulate_hessian_tensor_cores if tensor_cores else accumulate_hessian
+        self._accumulators = {layer: torch.zeros((self.input_size, self.input_size), dtype=torch.float32, device=device)
+                              for layer in self.selected}
+        self.denominators = {layer: 0.0 for layer in self.selected}
+        self.rows = {layer: 0 for layer in self.selected}
+        self.total_rows = {layer: 0 for layer in self.selected}
+        self.validation_rows = {layer: 0 for layer in self.selected}
+
+    def add_part(self, layers: torch.Tensor, split: torch.Tensor, observations: torch.Tensor, weights: torch.Tensor,
+                 values: torch.Tensor) -> None:
+        """One sample part: ``layers`` / ``split`` / ``observations`` / ``weights`` are ``[rows]``,
+        ``values`` is ``[rows, input_size]`` (any float dtype, host or device)."""
+
+        layers = layers.to(torch.int64)
+        split = split.to(torch.int8)
+        observations = observations.to(torch.int64)
+        weights = weights.to(torch.float32)
+        if not (layers.ndim == split.ndim == observations.ndim == weights.ndim == 1
+                and layers.numel() == split.numel() == observations.numel() == weights.numel()):
+            raise ValueError("sample part has invalid input metadata")
+        if tuple(values.shape) != (layers.numel(), self.input_size):
+            raise ValueError("sample part has invalid input.values shape")
+        if not bool(torch.all((split == 0) | (split == 1))):
+            raise ValueError("sample part has invalid input split labels")
+        epoch_mask = request_step_mask(observations, **self.request)
+        chosen = set(self.selected)
+        for raw_layer in torch.unique(layers).tolist():
+            layer = int(raw_layer)
+            if layer not in chosen:
+                continue
+            layer_mask = layers == layer
+            self.total_rows[layer] += int(layer_mask.sum())
+            self.validation_rows[layer] += int((layer_mask & (split == 1)).sum())
+            mask = layer_mask & epoch_mask
+            if self.split_value is not None:
+                mask &= split == self.split_value
+            indices = torch.nonzero(mask, as_tuple=False).flatten()
+            if not indices.numel():
+                continue
+            x = values.index_select(0, indices.to(values.device)).to(device=self.device, dtype=torch.float32)
+            w = weights.index_select(0, indices.to(weights.device)).to(device=self.device, dtype=torch.float32)
+            self._step(self._accumulators[layer], x, w, accumulate=True)
+            self.denominators[layer] += float(w.double().sum())
+            self.rows[layer] += int(indices.numel())
+
+    def finish(self, *, min_rows: int = 0, return_cpu: bool = True) -> dict[int, tuple[torch.Tensor, dict]]:
+        """``{layer: (H13, evidence)}``; the accumulators are consumed."""
+
+        out = {}
+        for layer in self.selected:
+            if self.rows[layer] < min_rows:
+                raise ValueError(f"layer {layer} has too few H13 rows: {self.rows[layer]}, minimum={min_rows}")
+            if self.denominators[layer] <= 0:
+                raise ValueError(f"layer {layer} has a non-positive H13 denominator")
+            h13 = finish_hessian(self._accumulators.pop(layer), self.denominators[layer])
+            if return_cpu:
+                h13 = h13.cpu().contiguous()
+            out[layer] = (h13, {"row": layer, "w13_rows": self.rows[layer], "w13_total_rows": self.total_rows[layer],
+                                "w13_validation_rows": self.validation_rows[layer],
+                                "w13_weight_sum": self.denominators[layer], "w2_prior": "identity", "w2_rows": 0})
+        return out

@@ -135,7 +135,7 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
                         sigma_reg: float = encoder.SIGMA_REG, tailbite_context: int = 128,
                         activation: str = "silu", down_from_reconstruction: bool = False,
                         score: bool = True, h2_max_local_alpha: float = 0.75,
-                        coupled_spec=None) -> list[ExpertPayload]:
+                        coupled_spec=None, shared_scale_scope=None) -> list[ExpertPayload]:
     """Encode a batch of experts at one uniform rate; see the module docstring for the flow.
 
     With ``coupled_spec`` (a ``coupled.CoupledHadamardSpec``) every expert is first moved into
@@ -143,7 +143,14 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
     with it (``transform_inputs``), the middle activation is evaluated through
     ``decode_middle`` and the routed error through ``decode_output``
     (``qsrt/pack/qsrt_candidates.py:1157-1180``); the payloads then describe the coupled
-    matrices."""
+    matrices.
+
+    ``shared_scale_scope`` switches on the shared input-scale mode of the production encoder for
+    the gate and up matrices (``shared_input_scales_key = (scope, matrix)`` with the global scale
+    folded into the output scales, qsrt/pack/qsrt_encoder.py:549-551): every expert encoded under
+    the scope stores the input-scale profile of the scope's first tensor, which is expert zero's
+    in a canonical layer encode.  A rank whose shard does not start with expert zero
+    calls ``prime_shared_scales`` with expert zero's weights first."""
 
     if not experts:
         return []
@@ -152,7 +159,16 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
         return _encode_coupled_batch(experts, coupled_spec, bits=bits, device=device, layer_seed=layer_seed,
                                      sigma_reg=sigma_reg, tailbite_context=tailbite_context,
                                      activation=activation, down_from_reconstruction=down_from_reconstruction,
-                                     score=score, h2_max_local_alpha=h2_max_local_alpha)
+                                     score=score, h2_max_local_alpha=h2_max_local_alpha,
+                                     shared_scale_scope=shared_scale_scope)
+
+    def shared(matrix: str) -> dict:
+        # gate and up only, with the global scale folded into the output scales so that the stored
+        # input scales really are one vector per layer and matrix (qsrt/pack/qsrt_encoder.py:549-551)
+        if shared_scale_scope is None or matrix not in ("w1", "w3"):
+            return {}
+        return {"shared_input_scales_key": (shared_scale_scope, matrix), "g_scale_into_sv": True}
+
     results: list[ExpertPayload] = []
     weights_sq = [ex.gates.float().square() for ex in experts]
 
@@ -163,13 +179,13 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
     a_weights, a_h, a_args = [], [], []
     for ex, w in zip(experts, weights_sq):
         h13, _ = hessian.weighted_covariance(ex.rows, w, device=device, return_cpu=False)
-        shared = encoder.make_shared_h(ex.w1.shape[1], device, h13)
+        shared_h = encoder.make_shared_h(ex.w1.shape[1], device, h13)
         del h13
-        for matrix, offset in ((ex.w1, 1), (ex.w3, 2)):
+        for matrix, offset, name in ((ex.w1, 1, "w1"), (ex.w3, 2, "w3")):
             a_weights.append(matrix.T.float().contiguous())
-            a_h.append(shared)
+            a_h.append(shared_h)
             a_args.append(quant_args_for(bits, device, seed=seed_of(ex, 0), sv_seed=seed_of(ex, offset),
-                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context))
+                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context, **shared(name)))
 
     def down_group(middles):
         b_weights, b_h, b_args, infos = [], [], [], []
@@ -180,7 +196,7 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
             b_h.append(encoder.make_shared_h(ex.w2.shape[1], device, h2))
             del h2
             b_args.append(quant_args_for(bits, device, seed=seed_of(ex, 3), sv_seed=seed_of(ex, 4),
-                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context))
+                                         sigma_reg=sigma_reg, tailbite_context=tailbite_context, **shared("w2")))
             b_weights.append(ex.w2.T.float().contiguous())
             infos.append(info)
         return (b_weights, b_h, b_args), infos
@@ -220,6 +236,26 @@ def encode_expert_batch(experts: list[ExpertSource], *, bits: int, device: torch
         for payload, (sse, energy) in zip(results, values.tolist()):
             payload.routed_sse, payload.routed_energy = sse, energy
     return results
+
+
+def prime_shared_scales(expert_zero: ExpertSource, *, bits: int, device: torch.device, shared_scale_scope,
+                        layer_seed: int = 0, sigma_reg: float = encoder.SIGMA_REG, tailbite_context: int = 128) -> None:
+    """Seed the shared input-scale profiles of a scope from expert zero's gate and up matrices.
+
+    Under ``shared_scale_scope`` every expert stores the input-scale profile of the scope's first
+    tensor - expert zero's in a canonical full-layer encode (qsrt/exl3_encoder_backend.py:2664-2672).
+    A rank whose shard does not begin with expert zero calls this once before its first encode,
+    as the reference's split workers re-encode expert zero as a primer
+    (scripts/pack_qsrt_candidates.py:1282, 1413-1425); only the part of the preparation that the
+    profile depends on is run.  ``expert_zero`` needs its weights only (rows may be empty)."""
+
+    device = torch.device(device)
+    for matrix, offset, name in ((expert_zero.w1, 1, "w1"), (expert_zero.w3, 2, "w3")):
+        args = quant_args_for(bits, device, seed=0,
+                              sv_seed=6 * (layer_seed * 100003 + expert_zero.expert_id) + offset, sigma_reg=sigma_reg,
+                              tailbite_context=tailbite_context, shared_input_scales_key=(shared_scale_scope, name),
+                              g_scale_into_sv=True)
+        encoder.prime_shared_input_scales(matrix.to(device).T.float().contiguous(), args)
 
 
 def score_payload(source: ExpertSource, payload: ExpertPayload, activation: str = "silu"):

@@ -484,6 +484,11 @@ def write_expert_atoms(
     FP16 scales (w1.svh, w3.svh, w2.suh).  Equals, byte for byte, packing each matrix, cutting
     it into logical atoms, rotating them and copying every atom to
     ``layout.atom_bundle_offset(slot, compressed_slot) + MATRIX_ATOM_TRELLIS_OFFSETS[m]``.
+
+    The closed-path check runs inside the packing pass, so a ``ValueError`` for states that are
+    not closed cyclic paths is raised after the expert's bundles have been written: the contents
+    of that compressed slot are then undefined and the caller must rewrite or discard the slot
+    (the reference validates before it produces a payload, ``qsrt/qsrt.py:916-1024``).
     """
 
     _image_view(image, layout)
@@ -499,6 +504,10 @@ def write_expert_atoms(
             if st.dtype == torch.bool or st.is_floating_point():
                 raise TypeError("encoded states must use an integer dtype")
             k_tiles, n_tiles, axis = _matrix_geometry(matrix, st)
+            if st.dtype in (torch.int32, torch.int64) and st.numel():
+                low, high = int(st.min()), int(st.max())
+                if low < -32768 or high > 65535:
+                    raise ValueError("encoded states do not fit 16 bits")
             st = st.to(device=image.device, dtype=torch.int16).contiguous()
             bits = _require_six_bit_pairs(resolve_mode(modes[matrix]))
             offset = base + MATRIX_ATOM_TRELLIS_OFFSETS[matrix]

@@ -355,3 +355,31 @@ def scoring_inputs(seed: int = 1618, rows: int = 96, hidden: int = 512, inter: i
     gates = torch.rand(rows, generator=g) * 0.5 + 0.05
     steps = torch.tensor([sorted(SCORING_REQUESTS)[i % 3] for i in range(rows)], dtype=torch.int64)
     return source, candidates, x, gates, steps
+
+
+# ---- capture -> Hessian streaming reducer case ------------------------------------------------------
+CAPTURE_CASE = {
+    "layers": 4, "input_size": 128, "selected": [1, 3],
+    "runs": {
+        "train_epochs_2_to_9": dict(sample_split="train", request_step_min=2, request_step_max=9, request_steps=None),
+        "all_listed_epochs": dict(sample_split="all", request_step_min=0, request_step_max=None, request_steps=[1, 4, 11]),
+    },
+}
+
+
+def capture_parts(seed: int = 2024, parts: int = 3, rows: int = 160):
+    """Seeded sample parts of a small capture: per part layer ids, split labels, observation ids
+    (request epoch in the high 32 bits), gate-square weights and bf16 input rows (CPU tensors)."""
+
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for part in range(parts):
+        layer = torch.randint(0, CAPTURE_CASE["layers"], (rows,), generator=g, dtype=torch.int32)
+        split = (torch.rand(rows, generator=g) < 0.25).to(torch.int8)
+        epoch = torch.randint(0, 13, (rows,), generator=g, dtype=torch.int64)
+        observation = (epoch << 32) | (torch.arange(rows, dtype=torch.int64) + part * rows)
+        weight = torch.rand(rows, generator=g) ** 2
+        values = (torch.randn((rows, CAPTURE_CASE["input_size"]), generator=g)
+                  * torch.exp(0.4 * torch.randn(CAPTURE_CASE["input_size"], generator=g))).to(torch.bfloat16)
+        out.append({"layer": layer, "split": split, "observation": observation, "weight": weight, "values": values})
+    return out

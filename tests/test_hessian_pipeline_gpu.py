@@ -353,3 +353,82 @@ def test_routed_input_hessian_errors(cuda_device):
         hessian.routed_input_hessian(x, -w, identity_shrinkage=0.1)
     with pytest.raises(ValueError, match="nonpositive mean diagonal"):
         hessian.routed_input_hessian(torch.zeros_like(x), w, identity_shrinkage=0.1)
+
+
+def test_shared_scale_profile_is_expert_zeros_on_every_rank(cuda_device):
+    """Shared input-scale mode under expert sharding (qsrt/exl3_encoder_backend.py:2664-2672,
+    scripts/pack_qsrt_candidates.py:1413-1425): a rank whose shard starts after expert zero must
+    store the very scale vectors a full-layer encode stores.  Rank 0 (experts 0, 1) and rank 1
+    (expert 2, primed with expert zero's weights) are played one after the other in this process,
+    each with an empty profile cache, and compared with the canonical one-process encode."""
+
+    from qsrt_b200 import encoder
+
+    experts = _tiny_experts(cuda_device, count=3)
+    kwargs = dict(bits=3, device=cuda_device, sigma_reg=1e-2, score=False, shared_scale_scope="layer7")
+    encoder.clear_shared_input_scales()
+    canonical = pipeline.encode_expert_batch(experts, **kwargs)
+    # gate and up of every expert carry |suh| of expert zero (the signs are per-expert draws, and
+    # the 1e-10 offset added before the sign-dependent rounding may move the last fp16 bit)
+    for payload in canonical[1:]:
+        for name in ("w1", "w3"):
+            got = getattr(payload, name).suh.abs().view(torch.int16).int()
+            want = getattr(canonical[0], name).suh.abs().view(torch.int16).int()
+            assert int((got - want).abs().max()) <= 1, name
+        assert not torch.equal(payload.w2.suh.abs(), canonical[0].w2.suh.abs())   # the down matrix keeps its own
+    encoder.clear_shared_input_scales()
+    rank0 = pipeline.encode_expert_batch(experts[:2], **kwargs)
+    encoder.clear_shared_input_scales()
+    pipeline.prime_shared_scales(experts[0], bits=3, device=cuda_device, shared_scale_scope="layer7", sigma_reg=1e-2)
+    rank1 = pipeline.encode_expert_batch(experts[2:], **kwargs)
+    encoder.clear_shared_input_scales()
+    unprimed = pipeline.encode_expert_batch(experts[2:], **kwargs)
+    encoder.clear_shared_input_scales()
+    for got, want in zip(rank0 + rank1, canonical):
+        for name in ("w1", "w3", "w2"):
+            a, b = getattr(got, name), getattr(want, name)
+            assert torch.equal(a.suh, b.suh) and torch.equal(a.svh, b.svh), name
+            # (tile grids: the feedback GEMMs of differently sized batches may round differently)
+            assert (a.trellis == b.trellis).all(dim=-1).float().mean().item() >= 0.97, name
+    # without the primer the shard would have stored its own first expert's profile
+    assert not torch.equal(unprimed[0].w1.suh, canonical[2].w1.suh)
+    with pytest.raises(NotImplementedError):
+        encoder.quantize_qsrt(torch.zeros((128, 128), device=cuda_device), encoder.make_shared_h(128, cuda_device),
+                              {"K": 3, "devices": [str(cuda_device)], "apply_out_scales": False,
+                               "return_trellis_diagnostics": True}, False)
+
+
+@pytest.mark.parametrize("tensor_cores", [False, True])
+def test_streaming_hessian_reducer_matches_reference(cuda_device, tensor_cores):
+    """tests/golden/capture_golden.npz holds what qsrt.capture._build_h13_identity_h2_streaming wrote
+    for the seeded three-part capture of tests.helpers.capture_parts (two selections of split and
+    request epochs); matrices to 1e-5 relative Frobenius, evidence numbers exactly."""
+
+    from pathlib import Path
+
+    from tests import helpers
+
+    golden = np.load(Path(__file__).parent / "golden" / "capture_golden.npz")
+    parts = helpers.capture_parts()
+    case = helpers.CAPTURE_CASE
+    for name, kwargs in case["runs"].items():
+        reducer = hessian.StreamingHessianReducer(case["input_size"], case["selected"], device=cuda_device,
+                                                  tensor_cores=tensor_cores, **kwargs)
+        for part in parts:
+            reducer.add_part(part["layer"], part["split"], part["observation"], part["weight"], part["values"])
+        result = reducer.finish(min_rows=4)
+        for layer in case["selected"]:
+            h13, evidence = result[layer]
+            want = golden[f"{name}_{layer}_h13"]
+            assert _rel_fro(h13, torch.from_numpy(want)) < 1e-5
+            assert torch.equal(h13, h13.T)
+            rows, total, validation, weight_sum = golden[f"{name}_{layer}_evidence"]
+            assert (evidence["w13_rows"], evidence["w13_total_rows"], evidence["w13_validation_rows"]) == (rows, total, validation)
+            assert abs(evidence["w13_weight_sum"] - weight_sum) <= 1e-12 * weight_sum
+    with pytest.raises(ValueError):
+        hessian.StreamingHessianReducer(128, [0], device=cuda_device).finish(min_rows=1)
+    with pytest.raises(ValueError):
+        hessian.StreamingHessianReducer(128, [0], device=cuda_device, sample_split="test")
+    bad = hessian.StreamingHessianReducer(128, [0], device=cuda_device)
+    with pytest.raises(ValueError):
+        bad.add_part(parts[0]["layer"], parts[0]["split"] + 2, parts[0]["observation"], parts[0]["weight"], parts[0]["values"])

@@ -83,3 +83,34 @@ def test_kernel_rejects_ragged_inputs_and_handles_empty():
     packed, scale = mo.seeded_source(45, 160, 9)
     got = mxfp4.dequant_encoder_orientation(torch.from_numpy(packed).cuda(), torch.from_numpy(scale).cuda())
     assert np.array_equal(got.cpu().numpy(), mo.dequant(packed, scale).T, equal_nan=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("round_bf16", [True, False])
+def test_fused_ingest_into_coupled_coordinates_is_bit_identical(round_bf16):
+    """MXFP4 source -> coupled coordinates in one pass per matrix equals dequantising (pinned
+    above to the reference's digests), optionally rounding to bfloat16 as a checkpoint holds the
+    source, and then ``encode_coupled_weights`` (pinned to the reference's digests in
+    tests/test_coupled.py), bit for bit."""
+
+    from qsrt_b200 import coupled
+
+    hidden, inter = 1024, 256
+    sources, dense = [], []
+    for index, (rows, cols) in enumerate(((inter, hidden), (inter, hidden), (hidden, inter))):
+        packed, scale = mo.seeded_source(rows, cols, 40 + index)
+        p, s = torch.from_numpy(packed).cuda(), torch.from_numpy(scale).cuda()
+        sources.append((p, s))
+        w = mxfp4.dequant(p, s)
+        dense.append(w.to(torch.bfloat16).float() if round_bf16 else w)
+    for draw in (0, 3):
+        spec = coupled.CoupledHadamardSpec(intermediate_draw=draw)
+        want = coupled.encode_coupled_weights(tuple(dense), spec)
+        got = coupled.encode_coupled_weights_mxfp4(tuple(sources), spec, round_bf16=round_bf16)
+        for a, b in zip(got, want):
+            assert a.shape == b.shape and torch.equal(a, b)
+    with pytest.raises(ValueError):
+        coupled.encode_coupled_weights_mxfp4((sources[0], sources[1], sources[1]), coupled.CoupledHadamardSpec())
+    with pytest.raises(TypeError):
+        coupled.encode_coupled_weights_mxfp4(((sources[0][0].float(), sources[0][1]), sources[1], sources[2]),
+                                             coupled.CoupledHadamardSpec())
