@@ -325,7 +325,14 @@ def run_b200(args) -> None:
     layer = Layer(args, device)
     shard = selection.assign_experts(layer.row_counts, world)[rank]
     per_gpu = args.experts_per_step
-    groups = [shard[i:i + per_gpu] for i in range(0, len(shard), per_gpu)]
+    # Groups are dealt from the shard sorted by routed rows, so that every step holds experts from
+    # each part of the Zipf-skewed row distribution and costs about the same (a few leading steps
+    # are then representative of the whole pass).
+    by_rows = sorted(shard, key=lambda e: (-layer.row_counts[e], e))
+    count = (len(shard) + per_gpu - 1) // per_gpu
+    chunks = [by_rows[q * count:(q + 1) * count] for q in range(per_gpu)]   # dealt back and forth
+    groups = [sorted(c[g] if q % 2 == 0 else c[len(c) - 1 - g] for q, c in enumerate(chunks) if g < len(c))
+              for g in range(count)]
     steps = args.steps if args.steps > 0 else len(groups)
     warmup = max(args.warmup, 3) if args.config == "c3" else max(args.warmup, 1)
     weights_per_expert = 3 * args.hidden * args.inter

@@ -57,9 +57,24 @@ chol_diag_kernel(float* __restrict__ a, int w, int ld, int first_column, int* __
     __shared__ int bad;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     if (t == 0) bad = 0;
-    for (int i = t; i < w * w; i += kThreads) {
-        const int r = i / w, c = i - r * w;
-        tile[r * kPitch + c] = a[int64_t(r) * ld + c];
+    if (w == kPanel) {
+        // a warp per row and iteration (512 contiguous bytes); all loads are issued before the
+        // first shared-memory store, so that their latencies overlap
+        constexpr int kRowsPerWarp = kPanel / (kThreads / 32);
+        float4 v[kRowsPerWarp];
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarp; ++i)
+            v[i] = *reinterpret_cast<const float4*>(a + int64_t(warp + i * (kThreads / 32)) * ld + 4 * lane);
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarp; ++i) {
+            float* dst = tile + (warp + i * (kThreads / 32)) * kPitch + 4 * lane;
+            dst[0] = v[i].x; dst[1] = v[i].y; dst[2] = v[i].z; dst[3] = v[i].w;
+        }
+    } else {
+        for (int i = t; i < w * w; i += kThreads) {
+            const int r = i / w, c = i - r * w;
+            tile[r * kPitch + c] = a[int64_t(r) * ld + c];
+        }
     }
     __syncthreads();
     for (int j0 = 0; j0 < w; j0 += kSub) {
@@ -74,16 +89,24 @@ chol_diag_kernel(float* __restrict__ a, int w, int ld, int first_column, int* __
                 const float p = __shfl_sync(0xffffffffu, row[c], c);
                 const bool ok = p > 0.0f && p <= 3.0e38f;   // also rejects NaN and infinity
                 if (!ok && lane == 0 && bad == 0) bad = first_column + j0 + c + 1;
-                // 1 / sqrt(p) once per column (correctly rounded division, then products): the serial
-                // part of the whole factorisation runs through these few instructions
-                const float inv = ok ? 1.0f / sqrtf(p) : 1.0f;
+                // 1 / sqrt(p) once per column, then products: the serial part of the whole
+                // factorisation runs through these few instructions.  Hardware estimate plus one
+                // Newton step (relative error about 1e-7, that of a rounded division).
+                float inv = 1.0f;
+                if (ok) {
+                    const float y = rsqrtf(p);
+                    inv = y * fmaf(-0.5f * p * y, y, 1.5f);
+                }
                 const float l = lane > c ? row[c] * inv : (lane == c ? p * inv : 0.0f);
                 if (lane == c) row_inv = inv;
                 row[c] = l;
 #pragma unroll
                 for (int k = c + 1; k < kSub; ++k) {
                     const float lk = __shfl_sync(0xffffffffu, l, k);
-                    if (lane >= k) row[k] = fmaf(-l, lk, row[k]);
+                    // (entries right of the diagonal, lane < k, are left as they are; written as
+                    // arithmetic, since a predicated store makes the compiler keep the row in
+                    // local memory)
+                    row[k] = fmaf(lane >= k ? -l : 0.0f, lk, row[k]);
                 }
             }
             if (lane < kSub) {
@@ -147,9 +170,22 @@ chol_diag_kernel(float* __restrict__ a, int w, int ld, int first_column, int* __
         if (t == 0) atomicCAS(status, 0, bad);
         return;
     }
-    for (int i = t; i < w * w; i += kThreads) {
-        const int r = i / w, c = i - r * w;
-        a[int64_t(r) * ld + c] = (c <= r) ? tile[r * kPitch + c] : tile[c * kPitch + r];
+    if (w == kPanel) {
+#pragma unroll 4
+        for (int r = warp; r < kPanel; r += kThreads / 32) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = 4 * lane + j;
+                v[j] = (c <= r) ? tile[r * kPitch + c] : tile[c * kPitch + r];
+            }
+            *reinterpret_cast<float4*>(a + int64_t(r) * ld + 4 * lane) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    } else {
+        for (int i = t; i < w * w; i += kThreads) {
+            const int r = i / w, c = i - r * w;
+            a[int64_t(r) * ld + c] = (c <= r) ? tile[r * kPitch + c] : tile[c * kPitch + r];
+        }
     }
 }
 
@@ -188,7 +224,7 @@ chol_panel_kernel(const float* __restrict__ diag, float* __restrict__ below, int
             float acc[kSub];
 #pragma unroll
             for (int i = 0; i < kSub; ++i) acc[i] = mine[c0 + i];
-#pragma unroll 2
+#pragma unroll 8
             for (int k = 0; k < c0; ++k) {
                 const float xv = mine[k];
 #pragma unroll

@@ -113,6 +113,10 @@ __device__ __forceinline__ float e2m1_times_scale(uint32_t code, float scale, in
     return v;
 }
 
+// Lane l of a warp owns VALS = 4 * SEGS consecutive values of the block (one 2 * SEGS-byte load of
+// codes); the butterflies keep the reference's order of widths (1, 2, 4, ... block / 2): the widths
+// below VALS run inside the lane's registers, the others across lanes by shuffles.  Which lane
+// holds which element does not change any sum, so the result equals the float32 kernel's.
 template <int SEGS>
 __global__ void __launch_bounds__(256)
 mxfp4_signed_hadamard_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
@@ -120,32 +124,61 @@ mxfp4_signed_hadamard_rows_kernel(const uint8_t* __restrict__ packed, const uint
                                   int row_offset, const float* __restrict__ signs, int round_bf16, float norm)
 {
     constexpr int BLOCK = 128 * SEGS;
+    constexpr int VALS = 4 * SEGS;      // 4, 8 or 16 consecutive values per lane
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int blocks_per_row = cols / BLOCK;
     if (warp >= rows * blocks_per_row) return;
     const int64_t r = warp / blocks_per_row;
-    const int c0 = int(warp - r * blocks_per_row) * BLOCK;
-    float v[SEGS][4];
+    const int c = int(warp - r * blocks_per_row) * BLOCK + lane * VALS;
+    uint32_t codes[(VALS + 7) / 8];
+    const uint8_t* src = packed + r * (cols / 2) + c / 2;
+    if constexpr (VALS == 4) codes[0] = *reinterpret_cast<const uint16_t*>(src);
+    else if constexpr (VALS == 8) codes[0] = *reinterpret_cast<const uint32_t*>(src);
+    else {
+        const uint2 two = *reinterpret_cast<const uint2*>(src);
+        codes[0] = two.x;
+        codes[1] = two.y;
+    }
+    const uint32_t byte = scale[r * (cols / 32) + c / 32];   // VALS <= 16 values never straddle a scale block
+    const float sc = __uint_as_float(byte == 0u ? 0x00400000u : byte << 23);
+    float v[VALS];
 #pragma unroll
-    for (int s = 0; s < SEGS; ++s) {
-        const int c = c0 + s * 128 + lane * 4;
-        const uint32_t codes = *reinterpret_cast<const uint16_t*>(packed + r * (cols / 2) + c / 2);
-        const uint32_t byte = scale[r * (cols / 32) + c / 32];
-        const float sc = __uint_as_float(byte == 0u ? 0x00400000u : byte << 23);
+    for (int i = 0; i < VALS; ++i) v[i] = e2m1_times_scale((codes[i >> 3] >> (4 * (i & 7))) & 15u, sc, round_bf16);
+    if (signs) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[s][i] = e2m1_times_scale((codes >> (4 * i)) & 15u, sc, round_bf16);
-        if (signs) {
-            const float4 g = *reinterpret_cast<const float4*>(signs + c);
-            v[s][0] *= g.x; v[s][1] *= g.y; v[s][2] *= g.z; v[s][3] *= g.w;
+        for (int q = 0; q < VALS / 4; ++q) {
+            const float4 g = *reinterpret_cast<const float4*>(signs + c + 4 * q);
+            v[4 * q] *= g.x; v[4 * q + 1] *= g.y; v[4 * q + 2] *= g.z; v[4 * q + 3] *= g.w;
         }
     }
-    butterflies<SEGS>(v, lane);
-    float* base = out + (r * row_step + row_offset) * ld + c0;
+    // widths 1 .. VALS / 2: inside the lane
 #pragma unroll
-    for (int s = 0; s < SEGS; ++s)
-        *reinterpret_cast<float4*>(base + s * 128 + lane * 4) =
-            make_float4(__fdiv_rn(v[s][0], norm), __fdiv_rn(v[s][1], norm), __fdiv_rn(v[s][2], norm), __fdiv_rn(v[s][3], norm));
+    for (int w = 1; w < VALS; w <<= 1) {
+#pragma unroll
+        for (int i = 0; i < VALS; ++i) {
+            if ((i & w) == 0) {
+                const float a = v[i], b = v[i | w];
+                v[i] = a + b;
+                v[i | w] = a - b;
+            }
+        }
+    }
+    // widths VALS .. block / 2: across lanes
+#pragma unroll
+    for (int bit = 1; bit < 32; bit <<= 1) {
+#pragma unroll
+        for (int i = 0; i < VALS; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], bit);
+            v[i] = (lane & bit) ? other - v[i] : v[i] + other;
+        }
+    }
+    float* base = out + (r * row_step + row_offset) * ld + c;
+#pragma unroll
+    for (int q = 0; q < VALS / 4; ++q)
+        *reinterpret_cast<float4*>(base + 4 * q) =
+            make_float4(__fdiv_rn(v[4 * q], norm), __fdiv_rn(v[4 * q + 1], norm), __fdiv_rn(v[4 * q + 2], norm),
+                        __fdiv_rn(v[4 * q + 3], norm));
 }
 
 // 128-row strips; `finish` applies the division and the trailing signs (single-pass blocks).
@@ -275,9 +308,9 @@ extern "C" int qsrtb_mxfp4_signed_block_hadamard(const uint8_t* packed, const ui
     if (cols % block_size) return qsrtb_fail(QSRTB_EINVAL, "Hadamard axis must be divisible by block_size");
     if (rows == 0 || cols == 0) return QSRTB_OK;
     if (!packed || !scale || !out) return qsrtb_fail(QSRTB_EINVAL, "null pointer");
-    if ((reinterpret_cast<uintptr_t>(packed) & 1) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+    if ((reinterpret_cast<uintptr_t>(packed) & 7) || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (signs && (reinterpret_cast<uintptr_t>(signs) & 15)))
-        return qsrtb_fail(QSRTB_EINVAL, "packed codes need 2-byte, output and signs 16-byte alignment");
+        return qsrtb_fail(QSRTB_EINVAL, "packed codes need 8-byte, output and signs 16-byte alignment");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const float norm = sqrtf(float(block_size));
     const int64_t warps = rows * (cols / block_size);

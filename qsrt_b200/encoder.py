@@ -919,6 +919,25 @@ def block_trace(A, B, block_size=1024):
     return total
 
 
+class HessianTrace:
+    """``trace(A.T @ H @ A)`` for several ``A`` against one symmetric ``H`` (the proxy error's
+    numerator and denominator, exl3_encoder_backend.py:2994-3025): ``H @ A`` is one tensor-core
+    product per ``A`` (``H`` is split into its operand planes once, its rows being its columns),
+    the contraction with ``A`` a float64 sum.  Returns 0-d float64 device tensors, so that a
+    caller can collect many traces before it synchronises."""
+
+    def __init__(self, H: torch.Tensor) -> None:
+        if H.ndim != 2 or H.shape[0] != H.shape[1] or not H.is_cuda or H.shape[0] % 4:
+            raise ValueError("the trace needs a square CUDA matrix whose size is a multiple of 4")
+        self.planes = _linalg.split_tf32(H.float().contiguous())
+
+    def __call__(self, A: torch.Tensor) -> torch.Tensor:
+        A = A.float()
+        product = torch.empty_like(A, memory_format=torch.contiguous_format)
+        _linalg.gemm_nt(self.planes, _linalg.split_tf32(A, transpose=True), product)
+        return torch.sum(product * A, dtype=torch.float64)
+
+
 def pack_trellis(encoded: torch.Tensor, quant_args: dict) -> torch.Tensor:
     """States [K/16, N/16, 256] -> packed words [K/16, N/16, 16*K] (exl3_encoder_backend.py:2361-2372)."""
 
@@ -1027,10 +1046,9 @@ def quantize_qsrt(weight: torch.Tensor, H_data: dict, quant_args: dict, return_w
         weight_q, encoded_q, mse_err = fallback_quant(weight_r, device, quant_args)
 
     if not q_fallback:
-        Hd = H.to(device)
-        num = block_trace(weight_r - weight_q, Hd)
-        den = block_trace(weight_r, Hd)
-        del Hd
+        trace = HessianTrace(H.to(device))
+        num, den = torch.stack((trace(weight_r - weight_q), trace(weight_r))).tolist()
+        del trace
         proxy_err = num / max(den, 1e-8)
     else:
         proxy_err = mse_err
@@ -1167,7 +1185,7 @@ def _uniform_finish(state):
     weight_r_stack, weight_q_stack, encoded_stack = state["weight_r"], state["weight_q"], state["encoded"]
     state["job"] = None  # drop the stacked factors
     for ri, run in enumerate(runs):
-        Hd = finalized[run[0]][0].to(device)
+        trace = HessianTrace(finalized[run[0]][0].to(device))
         col = 0
         for t in run:
             qa = quant_args_list[t]
@@ -1177,15 +1195,14 @@ def _uniform_finish(state):
             w_q = weight_q_stack[ri, :, col:col + width]
             enc = encoded_stack[ri, :, col // 16:(col + width) // 16]
             col += width
-            num = block_trace(w_r - w_q, Hd)
-            den = block_trace(w_r, Hd)
+            num, den = torch.stack((trace(w_r - w_q), trace(w_r))).tolist()
             proxy_err = num / max(den, 1e-8)
             suh = su.flatten().contiguous().to(dtype=torch.half, copy=True)
             svh = sv.flatten().contiguous().to(dtype=torch.half, copy=True)
             trellis = pack_trellis(enc.contiguous(), qa)
             qa.update({"apply_out_scales": apply_out_scales, "g_scale": state["g_scales"][t], "q_fallback": False})
             results[t] = (proxy_err, {"suh": suh, "svh": svh, "trellis": trellis})
-        del Hd
+        del trace
     return results
 
 
@@ -1293,14 +1310,15 @@ def quantize_qsrt_batch(weights: list[torch.Tensor], H_datas: list[dict], quant_
     encoded_all = [(weights_q[i:i + 1], encoded_q[i:i + 1]) for i in range(len(members))]
 
     results: list[list[dict]] = [[] for _ in range(source_count)]
-    denominators = [block_trace(item["weight_r"], item["H"]) for item in prepared]
+    traces = [HessianTrace(item["H"]) for item in prepared]
+    denominators = [float(trace(item["weight_r"])) for trace, item in zip(traces, prepared)]
     for (source, candidate), (weight_q, encoded) in zip(members, encoded_all):
         item = prepared[source]
         args = quant_args_groups[source][candidate]
         # dense-H path refinement per finished candidate (exl3_encoder_backend.py:3296-3312)
         weight_q, encoded, receipt = _refine().refine_uniform_h2_candidate(
             item["weight_r"], item["H"], weight_q[0], encoded[0], args)
-        numerator = block_trace(item["weight_r"] - weight_q, item["H"])
+        numerator = float(traces[source](item["weight_r"] - weight_q))
         if "suh" not in item:
             item["suh"] = item["su"].flatten().contiguous().to(dtype=torch.half, copy=True)
             item["svh"] = item["sv"].flatten().contiguous().to(dtype=torch.half, copy=True)
