@@ -22,8 +22,10 @@
 //                the stage's "empty" mbarrier and per segment to the accumulator's "ready" mbarrier;
 //   warps 2..5 : epilogue; each owns the 32 tensor-memory lanes (= rows of the tile) of its warp
 //                quadrant, adds the segments in registers and finally writes alpha * sum + beta * D,
-//                either row-major or transposed (D[n, m]), with row / column limits so that M and
-//                N need not be multiples of 128 (the loads rely on TMA's zero fill past the end).
+//                either row-major (through a shared-memory transpose, so that global memory is read
+//                and written in whole 512-byte row pieces) or transposed (D[n, m]), with row / column
+//                limits so that M and N need not be multiples of 128 (the loads rely on TMA's zero
+//                fill past the end).
 // No clusters and no multicast: all operands are this GPU's own memory.  Every mbarrier wait is
 // bounded; on expiry the kernel raises a status flag, lets its copies land, frees its tensor
 // memory and returns.
@@ -48,6 +50,8 @@ constexpr int kStages = 3;
 constexpr int kThreads = 192;
 constexpr int kSegmentSteps = 5;
 constexpr int kTileBytes = kTile * kBlockK * 4;
+constexpr int kStagePitch = kTile + 4;   // floats per row of the epilogue's staging block (16-byte aligned rows)
+static_assert(4 * 32 * kStagePitch * 4 <= 4 * kStages * kTileBytes, "the staging blocks must fit the operand stages");
 
 using Element = cutlass::tfloat32_t;
 
@@ -232,29 +236,49 @@ gemm3x_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p, TiledMM
             float* base = p.d + int64_t(z) * p.d_stride;
             const float alpha = p.alpha, beta = p.beta;
             if (!p.transposed_out) {
-                if (m < p.m) {
-                    float* row = base + int64_t(m) * p.ldd + n0;
-                    if (n0 + kTile <= p.n) {
+                // Through shared memory, so that global memory sees whole rows: a thread holds one
+                // row of the tile, but a warp that wrote its 32 rows directly would touch 32 rows
+                // with every 16-byte access.  Each epilogue warp parks its 32 x 128 block in its
+                // own part of the operand stages (idle by now: the last segment's MMAs have read
+                // them) and then moves it row by row, a lane per float4 = 512 contiguous bytes.
+                float* stage = reinterpret_cast<float*>(shared.operand[0].begin()) + q * (32 * kStagePitch);
 #pragma unroll
-                        for (int c = 0; c < kTile / 4; ++c) {
-                            float4 out = make_float4(alpha * total[4 * c], alpha * total[4 * c + 1],
-                                                     alpha * total[4 * c + 2], alpha * total[4 * c + 3]);
-                            float4* dst = reinterpret_cast<float4*>(row) + c;
+                for (int c = 0; c < kTile / 4; ++c)
+                    *reinterpret_cast<float4*>(stage + lane * kStagePitch + 4 * c) =
+                        make_float4(alpha * total[4 * c], alpha * total[4 * c + 1], alpha * total[4 * c + 2],
+                                    alpha * total[4 * c + 3]);
+                __syncwarp();
+                const int row0 = bi * kTile + q * 32;
+                const int col = n0 + 4 * lane;
+                if (col + 3 < p.n) {
+                    // all loads of the old values are issued before the first store (the rows are
+                    // independent; a row-by-row loop would wait for memory 32 times)
+                    const int rows_here = min(32, p.m - row0);
+                    float4 old[32];
+                    if (beta != 0.0f) {
+#pragma unroll
+                        for (int r = 0; r < 32; ++r)
+                            if (r < rows_here)
+                                old[r] = *reinterpret_cast<const float4*>(base + int64_t(row0 + r) * p.ldd + col);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) {
+                        if (r < rows_here) {
+                            float4 out = *reinterpret_cast<const float4*>(stage + r * kStagePitch + 4 * lane);
                             if (beta != 0.0f) {
-                                const float4 old = *dst;
-                                out.x = fmaf(beta, old.x, out.x); out.y = fmaf(beta, old.y, out.y);
-                                out.z = fmaf(beta, old.z, out.z); out.w = fmaf(beta, old.w, out.w);
+                                out.x = fmaf(beta, old[r].x, out.x); out.y = fmaf(beta, old[r].y, out.y);
+                                out.z = fmaf(beta, old[r].z, out.z); out.w = fmaf(beta, old[r].w, out.w);
                             }
-                            *dst = out;
+                            *reinterpret_cast<float4*>(base + int64_t(row0 + r) * p.ldd + col) = out;
                         }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < kTile; ++c) {
-                            if (n0 + c < p.n) {
-                                float out = alpha * total[c];
-                                if (beta != 0.0f) out = fmaf(beta, row[c], out);
-                                row[c] = out;
-                            }
+                    }
+                } else if (col < p.n) {
+                    for (int r = 0; r < 32 && row0 + r < p.m; ++r) {
+                        for (int i = 0; i < 4 && col + i < p.n; ++i) {
+                            float* dst = base + int64_t(row0 + r) * p.ldd + col + i;
+                            float out = stage[r * kStagePitch + 4 * lane + i];
+                            if (beta != 0.0f) out = fmaf(beta, *dst, out);
+                            *dst = out;
                         }
                     }
                 }
