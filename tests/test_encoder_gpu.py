@@ -497,3 +497,48 @@ def test_full_size_teacher_forced_identity_with_library_products(cuda_device):
     identity, worst = _teacher_forced_against_reference_kernel(cuda_device, 3, ldlq_tensor_cores=False)
     assert identity >= 0.9999, f"tile identity {identity:.5f}"
     assert worst <= 0.1
+
+
+# ---- the module handed to a reference caller ---------------------------------------------------------
+@pytest.mark.parametrize("bits,hessian", [(3, True), (2, False)])
+def test_module_serves_the_uniform_candidate_caller(cuda_device, bits, hessian):
+    """What ``encode_uniform_candidate`` (qsrt/qsrt_codec_pilot.py:284-520) does with its
+    ``quantizer_module``, step for step: the ``quant_args`` it builds (:421-452, TF32 feedback
+    allowed and an explicit feedback multiplier included), ``make_shared_h`` with or without a
+    caller Hessian (:391-418), the positional call (:456-462) and every check it then applies to
+    what comes back (:466-478 payload shapes and dtypes, :497-507 closure and decode through the
+    uniform unpacker, :515-519 payload size equals the declared rate, finite proxy)."""
+
+    quantizer_module = encoder
+    gate, capture = _tiny_expert(1400 + bits)
+    source = gate                                            # [out, in], as the caller receives it
+    encoder_weight = source.T.float().contiguous().to(cuda_device)
+    shared_h = quantizer_module.make_shared_h(encoder_weight.shape[0], cuda_device, capture if hessian else None)
+    quant_args = {
+        "K": bits, "seed": 1_000_002, "sv_seed": 1_499_981, "sigma_reg": 0.025, "devices": [str(cuda_device)],
+        "device_ratios": None, "apply_out_scales": False, "ldlq_tf32": True, "tailbite_context": 128,
+        "ldlq_feedback_multiplier": 1.0, "sqg_e4m3_lut": tables.sqg_codebook_bytes(bits, tables.SQG_XOR_CHEB_T12),
+    }
+    torch.cuda.synchronize(cuda_device)
+    _, proxy, tensors = quantizer_module.quantize_qsrt(encoder_weight, shared_h, quant_args, False, progress_str="")
+    torch.cuda.synchronize(cuda_device)
+    trellis, suh, svh = tensors["trellis"].contiguous(), tensors["suh"].contiguous(), tensors["svh"].contiguous()
+    assert trellis.dtype == torch.int16
+    assert tuple(trellis.shape) == (encoder_weight.shape[0] // 16, encoder_weight.shape[1] // 16, 16 * bits)
+    assert suh.dtype == torch.float16 and tuple(suh.shape) == (encoder_weight.shape[0],)
+    assert svh.dtype == torch.float16 and tuple(svh.shape) == (encoder_weight.shape[1],)
+    states = codec.unpack_trellis_states(trellis, bits)
+    assert oracle.states_close(states.cpu().numpy(), bits)
+    decoded = codec.decode_exl3_weight(states, suh, svh, bits=bits).half()
+    reconstruction = decoded.T.contiguous().cpu()
+    assert reconstruction.shape == source.shape
+    assert trellis.numel() * trellis.element_size() * 8.0 / source.numel() == float(bits)
+    assert np.isfinite(float(proxy)) and quant_args["g_scale"] > 0 and quant_args["q_fallback"] is False
+    rel = float(((reconstruction.float() - source) ** 2).mean() / (source ** 2).mean())
+    assert rel < (0.12 if bits == 2 else 0.04)
+    # research arms the caller can ask for are refused by name, before any work is done
+    for key in ("return_trellis_diagnostics", "use_two_sided_traversal_without_output_feedback"):
+        with pytest.raises(NotImplementedError):
+            quantizer_module.quantize_qsrt(source.T.float().contiguous().to(cuda_device),
+                                           quantizer_module.make_shared_h(512, cuda_device), dict(quant_args, **{key: True}),
+                                           False, progress_str="")
