@@ -426,25 +426,26 @@ def test_quantize_qsrt_against_reference_run(cuda_device, monkeypatch, name):
 
 
 # ---- full-size teacher-forced identity against the unmodified reference kernel -------------------------
-def _full_size_case(device, bits):
-    """One gate-shaped matrix of the full layer ([in 7168, out 2048]) and a routed-rows Hessian
-    (1536 rows: rank-deficient before damping, like the layer's average expert)."""
+def _full_size_case(device, bits, k=7168, n=2048):
+    """One matrix of the full layer in encoder orientation - gate-shaped [in 7168, out 2048] or
+    down-shaped [in 2048, out 7168] - and a routed-rows Hessian (1536 rows: rank-deficient before
+    damping for the gate shape, like the layer's average expert)."""
 
-    g = torch.Generator().manual_seed(31000 + bits)
-    weight = (torch.randn((7168, 2048), generator=g) * 0.02).to(device)
+    g = torch.Generator().manual_seed(31000 + bits + k)
+    weight = (torch.randn((k, n), generator=g) * 0.02).to(device)
     gd = torch.Generator(device=device).manual_seed(31001)
-    rows = torch.randn((1536, 7168), generator=gd, device=device)
-    rows *= torch.exp(0.5 * torch.randn(7168, generator=gd, device=device))
+    rows = torch.randn((1536, k), generator=gd, device=device)
+    rows *= torch.exp(0.5 * torch.randn(k, generator=gd, device=device))
     hessian = (rows.T @ rows / rows.shape[0]).float()
     return weight, hessian
 
 
-def _teacher_forced_against_reference_kernel(device, bits, **extra_args):
+def _teacher_forced_against_reference_kernel(device, bits, shape=(7168, 2048), **extra_args):
     if helpers.reference_extension() is None:
         pytest.skip("the reference tile-encoder extension (oracle/_ref) is not built")
-    weight, hessian = _full_size_case(device, bits)
+    weight, hessian = _full_size_case(device, bits, *shape)
     args = _quant_args(bits, device, sigma_reg=0.025, **extra_args)
-    h_data = encoder.make_shared_h(7168, device, hessian)
+    h_data = encoder.make_shared_h(shape[0], device, hessian)
     del hessian
     _, proxy, tensors = encoder.quantize_qsrt(weight, h_data, args, False)
     lut = args["sqg_e4m3_lut"]
@@ -486,6 +487,14 @@ def test_full_size_teacher_forced_identity_vs_reference_kernel(cuda_device, bits
     asserted as a sanity bound."""
 
     identity, worst = _teacher_forced_against_reference_kernel(cuda_device, bits)
+    assert identity >= 0.999, f"tile identity {identity:.5f}"
+    assert worst <= 0.1
+
+
+def test_full_size_teacher_forced_identity_down_shape_k4(cuda_device):
+    """The down projection's shape ([in 2048, out 7168]: 16 spans of 448-tile rows) at K4."""
+
+    identity, worst = _teacher_forced_against_reference_kernel(cuda_device, 4, shape=(2048, 7168))
     assert identity >= 0.999, f"tile identity {identity:.5f}"
     assert worst <= 0.1
 
