@@ -54,16 +54,27 @@ int qsrtb_lut_prepare(const uint8_t* lut_state, int bits, uint8_t* lut_pm, float
  * bit-identical to them.
  *
  * qsrtb_viterbi_scratch_bytes: bytes of traceback scratch wanted for `n_tiles` tiles on the
- * current device (a persistent grid is used, so this saturates at one slice per resident CTA).
+ * current device (a persistent grid is used, so this saturates at one slice per resident CTA:
+ * 0.5 or 1 MiB of survivor decisions at 2 bits or when no CTA gets a second tile, else two
+ * slots of 256 path-cost rows, 4 MiB at 4 bits and 8 MiB at 3).  A call given less scratch than
+ * that still works: it keeps survivor decisions for every step, on as many CTAs as the scratch
+ * has slices.
  */
 int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 
 /* `variant` of the search entry points: bit 0 = dedicated K2 arithmetic (bits == 2 only);
  * bits 4-5 = thread layout of the search kernel, a per-call tuning choice without a reference
  * counterpart (0 = per-rate default, 1 = 1024 threads holding fp8 labels, 2 = 512 threads
- * holding half2 labels in registers).  Results are identical for every layout. */
+ * holding half2 labels in registers); bits 6-7 = what the search keeps for its traceback, also
+ * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = for the
+ * constrained pass of all but a CTA's last tile the path costs, from which the traceback
+ * recomputes the one decision per step it needs while the next tile is searched; 0 = 2 where it
+ * pays: 3 or 4 bits, tailbite_context 128, more tiles than SMs, scratch as
+ * qsrtb_viterbi_scratch_bytes says; an explicit 2 needs 2 * 256 * 2^(17 - bits) bytes per CTA).
+ * Results are identical for every layout and organisation. */
 #define QSRTB_VARIANT_DEDICATED_K2 1
 #define QSRTB_VARIANT_LAYOUT(units) ((units) << 4)
+#define QSRTB_VARIANT_TRACEBACK(organisation) ((organisation) << 6)
 
 int qsrtb_quantize_tiles(const float* tiles,        /* [n_tiles, 256] tensor-core order   */
                          int64_t n_tiles,

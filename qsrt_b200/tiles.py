@@ -86,11 +86,13 @@ def prepared_table(codebook: torch.Tensor, bits: int, device: torch.device):
     return lut, lut_pm, abs_max
 
 
-def traceback_scratch(device: torch.device, bits: int) -> torch.Tensor:
-    """Survivor scratch of the current stream: one slice per resident CTA of the persistent
-    grid.  Keyed by stream so that searches enqueued on different streams never share rows."""
+def traceback_scratch(device: torch.device, bits: int, cost_rows: bool = False) -> torch.Tensor:
+    """Traceback scratch of the current stream: one slice per resident CTA of the persistent
+    grid.  Keyed by stream so that searches enqueued on different streams never share rows.
+    ``cost_rows`` asks for the two slots of path-cost rows per CTA that an explicit
+    ``traceback=2`` needs at every rate (the default size already has them at 3 and 4 bits)."""
 
-    key = (str(device), bits, torch.cuda.current_stream(device).cuda_stream)
+    key = (str(device), bits, torch.cuda.current_stream(device).cuda_stream, bool(cost_rows))
     buffer = _scratch.get(key)
     if buffer is None:
         wanted = ctypes.c_size_t(0)
@@ -99,7 +101,11 @@ def traceback_scratch(device: torch.device, bits: int) -> torch.Tensor:
                 _lib.lib().qsrtb_viterbi_scratch_bytes(bits, 1 << 30, ctypes.byref(wanted)),
                 "qsrtb_viterbi_scratch_bytes",
             )
-        buffer = torch.empty(wanted.value, dtype=torch.uint8, device=device)
+        size = wanted.value
+        if cost_rows:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            size = max(size, sms * 2 * 256 * (2 << (16 - bits)))
+        buffer = torch.empty(size, dtype=torch.uint8, device=device)
         _scratch[key] = buffer
     return buffer
 
@@ -112,12 +118,15 @@ def encode_tiles(
     *,
     force_generic: bool = False,
     units_per_thread: int = 0,
+    traceback: int = 0,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Encode ``[N, 256]`` float32 CUDA tiles with a state-indexed E4M3 table.
 
     ``units_per_thread`` picks the search kernel's thread layout for this call (0 = per-rate
-    default, 1 = 1024 threads with fp8 labels, 2 = 512 threads with half2 labels); the results
-    do not depend on it."""
+    default, 1 = 1024 threads with fp8 labels, 2 = 512 threads with half2 labels) and
+    ``traceback`` what the kernel keeps for its traceback (0 = the kernel's choice, 1 = survivor
+    decisions, 2 = path costs with the decisions recomputed lazily); the results do not depend
+    on either."""
 
     if not tiles.is_cuda:
         raise ValueError("input_tiles must be CUDA")
@@ -129,6 +138,8 @@ def encode_tiles(
         raise ValueError("tailbite_context must be in 1..128")
     if units_per_thread not in (0, 1, 2):
         raise ValueError("units_per_thread must be 0 (per-rate default), 1 or 2")
+    if traceback not in (0, 1, 2):
+        raise ValueError("traceback must be 0 (kernel's choice), 1 (decisions) or 2 (path costs)")
     tiles = tiles.contiguous()
     device = tiles.device
     lut, lut_pm, abs_max = prepared_table(codebook, bits, device)
@@ -142,12 +153,13 @@ def encode_tiles(
     indices = torch.empty_like(tiles, dtype=torch.int16)
     if tiles.shape[0] == 0:
         return output, indices
-    scratch = traceback_scratch(device, bits)
+    scratch = traceback_scratch(device, bits, cost_rows=traceback == 2)
     with torch.cuda.device(device), timed_search(device, tiles.shape[0], bits):
         _lib.check(
             _lib.lib().qsrtb_quantize_tiles(
                 tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits,
-                int(tailbite_context), (1 if dedicated else 0) | (int(units_per_thread) << 4), output.data_ptr(),
+                int(tailbite_context), (1 if dedicated else 0) | (int(units_per_thread) << 4) | (int(traceback) << 6),
+                output.data_ptr(),
                 indices.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream_ptr(device),
             ),
             "qsrtb_quantize_tiles",

@@ -115,6 +115,45 @@ def test_thread_layouts_agree(cuda_device, bits):
     assert np.array_equal(idx2.cpu().numpy()[:8], ref_idx)
 
 
+@pytest.mark.parametrize("context", [1, 32, 128])
+@pytest.mark.parametrize("bits,generic", [(2, False), (2, True), (3, False), (4, False)])
+def test_traceback_organisations_agree(cuda_device, bits, generic, context):
+    """Survivor decisions for every step, or path costs for the constrained pass with the one
+    decision per step recomputed by the traceback chain: same states, same reconstruction.  The
+    batch gives every CTA several tiles (chains overlapping the next tile), includes rows that
+    meet the fp16 clamp (re-encoded with the literal arithmetic while a chain is in flight) and
+    contexts whose primer is too short to hide a chain (the rest is walked at the end)."""
+
+    tiles = helpers.mixed_tiles(160, seed=11 * bits + context).to(cuda_device)
+    tiles[5::37] *= 60.0
+    lut = _lut(bits)
+    for units in (1, 2):
+        kept = tile_api.encode_tiles(tiles, lut, bits, context, force_generic=generic,
+                                     units_per_thread=units, traceback=1)
+        lazy = tile_api.encode_tiles(tiles, lut, bits, context, force_generic=generic,
+                                     units_per_thread=units, traceback=2)
+        same = (kept[1] == lazy[1]).all(dim=1)
+        assert bool(same.all()), f"units {units}: {int((~same).sum())} of {tiles.shape[0]} tiles differ"
+        assert torch.equal(kept[0], lazy[0])
+    chosen = tile_api.encode_tiles(tiles, lut, bits, context, force_generic=generic)
+    assert torch.equal(chosen[1], kept[1])
+
+
+def test_lazy_traceback_matches_reference_kernel(cuda_device):
+    """The path-cost organisation against the unmodified reference kernel, every family."""
+
+    if helpers.reference_extension() is None:
+        pytest.skip("oracle/_ref was not built")
+    for bits in (2, 3, 4):
+        lut = _lut(bits)
+        tiles = torch.cat([helpers.make_tiles(f, 400, seed=41 + bits) for f in helpers.FAMILIES]).to(cuda_device)
+        out, idx = tile_api.encode_tiles(tiles, lut, bits, 128, traceback=2)
+        ref_out, ref_idx = helpers.reference_quantize_tiles(tiles, lut, bits, 128)
+        same = (idx == ref_idx).all(dim=1)
+        assert bool(same.all()), f"K{bits}: {int((~same).sum())} of {tiles.shape[0]} tiles differ"
+        assert torch.equal(out, ref_out)
+
+
 def test_empty_and_ragged_batches(cuda_device):
     lut = _lut(3)
     out, idx = tile_api.encode_tiles(torch.empty((0, 256), device=cuda_device), lut, 3)
