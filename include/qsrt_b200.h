@@ -64,8 +64,8 @@ int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 
 /* `variant` of the search entry points: bit 0 = dedicated K2 arithmetic (bits == 2 only);
  * bits 4-5 = thread layout of the search kernel, a per-call tuning choice without a reference
- * counterpart (0 = per-rate default, 1 = 1024 threads holding fp8 labels, 2 = 512 threads
- * holding half2 labels in registers); bits 6-7 = what the search keeps for its traceback, also
+ * counterpart (0 = the faster one for the rate and traceback organisation, 1 = 1024 threads
+ * holding fp8 labels, 2 = 512 threads holding half2 labels in registers); bits 6-7 = what the search keeps for its traceback, also
  * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = for the
  * constrained pass of all but a CTA's last tile the path costs, from which the traceback
  * recomputes the one decision per step it needs while the next tile is searched; 0 = 2 where it

@@ -41,18 +41,20 @@ def main() -> None:
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--seed", type=int, default=20260816)
     p.add_argument("--units", type=int, default=0, help="work units per thread of the search kernel (0 auto, 1 or 2)")
+    p.add_argument("--traceback", type=int, default=0,
+                   help="what the kernel keeps for its traceback (0 its own choice, 1 decisions, 2 path costs)")
     args = p.parse_args()
     device = torch.device("cuda:0")
     x = make_tiles(args.family, args.tiles, args.seed).to(device)
     lut = tables.sqg_xor_cheb_t12_bytes(args.bits)
     for _ in range(args.warmup):
-        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units)
+        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units, traceback=args.traceback)
     torch.cuda.synchronize()
     times = []
     for _ in range(args.iters):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units)
+        tile_api.encode_tiles(x, lut, args.bits, args.context, units_per_thread=args.units, traceback=args.traceback)
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
@@ -60,7 +62,7 @@ def main() -> None:
     metrics = args.tiles * (256 + 2 * args.context) * METRICS_PER_STEP
     print(json.dumps({
         "tiles": args.tiles, "bits": args.bits, "context": args.context, "family": args.family, "units": args.units,
-        "median_ms": ms, "ktiles_per_s": args.tiles / ms, "mweights_per_s": args.tiles * 256 / ms / 1e3,
+        "traceback": args.traceback, "median_ms": ms, "ktiles_per_s": args.tiles / ms, "mweights_per_s": args.tiles * 256 / ms / 1e3,
         "g_branch_metrics_per_s": metrics / ms / 1e6,
     }))
 

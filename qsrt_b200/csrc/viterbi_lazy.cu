@@ -33,7 +33,7 @@ namespace {
 
 using namespace qsrtb_vit;
 
-constexpr int kChainCadence = 2;  // trellis steps between two links of a chain
+constexpr int kChainCadence = 2;  // trellis steps between two links of a chain (even: see run_pass)
 constexpr int kChainWarp = 0;      // the warp that walks the chain (any does equally well)
 
 // The traceback in flight: the constrained pass of tile `tile`, whose cost rows are in `slot`.
@@ -320,13 +320,18 @@ __device__ __forceinline__ int encode_tile_lazy(const uint32_t (&L)[UNITS][NL], 
             }
             __syncthreads();
         }
-        for (int i = 0; i < steps; ++i) {
+        // Every pass has an even number of steps, so the step counter is even after the second
+        // step of each pair below: the chain, whose links fall due on even counts, is looked at
+        // there only.
+        auto step = [&](const int i, auto chain_tag) {
             const int ri = (i + roll) & 255;
             ++cx.tick;
-            if (warp == kChainWarp && cx.tick == cx.chain_due) {
-                const bool more = chain_link<K, CHAIN_MODE>(&sm->chain, sm, cx.slot_base, cx.slot_bytes,
-                                                            cx.labels, lane);
-                cx.chain_due = more ? cx.tick + kChainCadence : kNever;
+            if constexpr (decltype(chain_tag)::value) {
+                if (cx.tick == cx.chain_due) {  // kNever in every warp but the chain's
+                    const bool more = chain_link<K, CHAIN_MODE>(&sm->chain, sm, cx.slot_base, cx.slot_bytes,
+                                                                cx.labels, lane);
+                    cx.chain_due = more ? cx.tick + kChainCadence : kNever;
+                }
             }
             __half* t = cur; cur = inc; inc = t;
             const __half w = sm->in_h[slot][ri];
@@ -363,6 +368,10 @@ __device__ __forceinline__ int encode_tile_lazy(const uint32_t (&L)[UNITS][NL], 
             }
             if constexpr (MODE == MODE_K2) k2_publish(i, step_min2);
             __syncthreads();
+        };
+        for (int i = 0; i < steps; i += 2) {
+            step(i, std::false_type{});
+            step(i + 1, std::true_type{});
         }
     };
     auto clamp_met = [&]() {
@@ -403,7 +412,7 @@ __device__ __forceinline__ int encode_tile_lazy(const uint32_t (&L)[UNITS][NL], 
             __syncwarp();
             chain_issue<K>(ch, 255, end_state, slot_rows, lane);
         }
-        cx.chain_due = cx.tick + kChainCadence;
+        cx.chain_due = warp == kChainWarp ? cx.tick + kChainCadence : kNever;
         __syncthreads();
         return 2;
     }
