@@ -537,16 +537,17 @@ def run_b200(args) -> None:
         "clocks": clocks,
         "roofline": {
             "bound": "alu",
-            "kernel": f"viterbi_kernel<{args.bits}>",
+            "kernel": SEARCH_KERNEL[args.bits],
             "achieved": achieved,
             "peak": peak,
             "unit": "G branch metrics/s",
             "frac": achieved / peak if peak > 0 else None,
-            # DRAM bytes per launch: one ncu capture of this kernel on 592 tiles measured
-            # 1 107.7 MB read + written = 1.871 MB per tile (the survivor rows); the traffic grows
-            # in proportion to the tiles, so it is scaled to this run's average launch.
-            "traffic": NCU_DRAM_BYTES_PER_TILE * search_tiles / max(search_launches, 1),
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 592-tile launch, scaled per tile",
+            # DRAM bytes per launch: one ncu capture of this kernel measured the bytes read + written
+            # per tile below (survivor decisions and, at three and four bits, path-cost rows); the
+            # traffic grows in proportion to the tiles, so it is scaled to this run's average launch.
+            "traffic": (NCU_DRAM_BYTES_PER_TILE[args.bits] * search_tiles / max(search_launches, 1)
+                        if NCU_DRAM_BYTES_PER_TILE[args.bits] else None),
+            "traffic_source": NCU_DRAM_SOURCE[args.bits],
             "algorithmic_dram_bytes_per_tile": 4 * 256 * 4 + 256 * 2,  # rows + compensation in, reconstruction + error + states out
             "peak_source": "of live probe: half2 FMA lanes/s measured in this run / 3 half operations per branch metric "
                            "(the driver's measured-peaks file holds no ALU figure)",
@@ -698,7 +699,23 @@ def cpu_baseline(payload, bits: int) -> dict:
     }
 
 
-NCU_DRAM_BYTES_PER_TILE = (817.4e6 + 290.3e6) / 592
+# The search kernel a layer-sized launch gets at each rate, and its DRAM bytes per tile from the
+# ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
+SEARCH_KERNEL = {
+    2: "viterbi_kernel<2, dedicated, 2 units/thread> (survivor decisions)",
+    3: "viterbi_lazy_kernel<3, generic, 2 units/thread> (path costs in the constrained pass)",
+    4: "viterbi_lazy_kernel<4, generic, 2 units/thread> (path costs in the constrained pass)",
+}
+NCU_DRAM_BYTES_PER_TILE = {
+    2: (823.1e6 + 337.3e6) / 592,
+    3: (4906.3e6 + 412.0e6) / 1184,
+    4: None,
+}
+NCU_DRAM_SOURCE = {
+    2: "ncu capture of a 592-tile launch, scaled per tile",
+    3: "ncu capture of a 1184-tile launch (8 tiles per CTA), scaled per tile",
+    4: "not captured (half of the three-bit figure by construction: rows of 4096 states)",
+}
 
 
 def main() -> None:
