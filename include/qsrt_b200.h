@@ -55,22 +55,25 @@ int qsrtb_lut_prepare(const uint8_t* lut_state, int bits, uint8_t* lut_pm, float
  *
  * qsrtb_viterbi_scratch_bytes: bytes of traceback scratch wanted for `n_tiles` tiles on the
  * current device (a persistent grid is used, so this saturates at one slice per resident CTA:
- * 0.5 or 1 MiB of survivor decisions at 2 bits or when no CTA gets a second tile, else two
- * slots of 256 path-cost rows, 4 MiB at 4 bits and 8 MiB at 3).  A call given less scratch than
+ * 0.5 or 1 MiB of survivor decisions at 2 bits or when no CTA gets a second tile, else the
+ * path-cost rows of qsrtb_viterbi_cost_scratch_bytes, 6 MiB at 4 bits and 12 MiB at 3).  A call given less scratch than
  * that still works: it keeps survivor decisions for every step, on as many CTAs as the scratch
  * has slices.
  */
 int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
+/* The scratch an explicit QSRTB_VARIANT_TRACEBACK(2) needs at any rate: two buffers of 256 and
+ * two of 130 path-cost rows per resident CTA (6 / 12 / 24 MiB at 4 / 3 / 2 bits). */
+int qsrtb_viterbi_cost_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 
 /* `variant` of the search entry points: bit 0 = dedicated K2 arithmetic (bits == 2 only);
  * bits 4-5 = thread layout of the search kernel, a per-call tuning choice without a reference
  * counterpart (0 = the faster one for the rate and traceback organisation, 1 = 1024 threads
  * holding fp8 labels, 2 = 512 threads holding half2 labels in registers); bits 6-7 = what the search keeps for its traceback, also
- * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = for the
- * constrained pass of all but a CTA's last tile the path costs, from which the traceback
- * recomputes the one decision per step it needs while the next tile is searched; 0 = 2 where it
- * pays: 3 or 4 bits, tailbite_context 128, more tiles than SMs, scratch as
- * qsrtb_viterbi_scratch_bytes says; an explicit 2 needs 2 * 256 * 2^(17 - bits) bytes per CTA).
+ * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = path
+ * costs, from which the tracebacks recompute the one decision per step they need while the
+ * passes of the CTA's next tiles run - all passes but the constrained ones of a CTA's last two
+ * tiles; 0 = 2 where it pays: 3 or 4 bits, tailbite_context 128, more tiles than SMs, scratch
+ * as qsrtb_viterbi_scratch_bytes says; an explicit 2 needs qsrtb_viterbi_cost_scratch_bytes).
  * Results are identical for every layout and organisation. */
 #define QSRTB_VARIANT_DEDICATED_K2 1
 #define QSRTB_VARIANT_LAYOUT(units) ((units) << 4)

@@ -22,6 +22,7 @@ _SIGNATURES = {
     "qsrtb_probe_half2_fma": (_c.c_int, [_c.c_int, _PTR, _c.POINTER(_c.c_double), _PTR]),
     "qsrtb_lut_prepare": (_c.c_int, [_PTR, _c.c_int, _PTR, _PTR, _PTR]),
     "qsrtb_viterbi_scratch_bytes": (_c.c_int, [_c.c_int, _c.c_int64, _c.POINTER(_c.c_size_t)]),
+    "qsrtb_viterbi_cost_scratch_bytes": (_c.c_int, [_c.c_int, _c.c_int64, _c.POINTER(_c.c_size_t)]),
     "qsrtb_quantize_tiles": (
         _c.c_int,
         [_PTR, _c.c_int64, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _PTR, _PTR, _PTR, _c.c_size_t, _PTR],
@@ -122,6 +123,7 @@ _KERNELS_PER_CALL = {
     "qsrtb_abi_version": 0,
     "qsrtb_last_error": 0,
     "qsrtb_viterbi_scratch_bytes": 0,
+    "qsrtb_viterbi_cost_scratch_bytes": 0,
     "qsrtb_hessian_tc_workspace_bytes": 0,
     "qsrtb_cholesky_workspace_bytes": 0,
     # per 128-column panel: diagonal block, rows below it, trailing update (the last has only the first)

@@ -349,6 +349,16 @@ extern "C" int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* by
     return QSRTB_OK;
 }
 
+extern "C" int qsrtb_viterbi_cost_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes)
+{
+    if (bits < 2 || bits > 4 || !bytes || n_tiles < 0) return qsrtb_fail(QSRTB_EINVAL, "bad scratch query");
+    const int sms = resident_ctas();
+    if (sms <= 0) return qsrtb_fail(QSRTB_ECUDA, "cannot query the device");
+    const int64_t grid = n_tiles < sms ? n_tiles : sms;
+    *bytes = size_t(grid > 0 ? grid : 1) * qsrtb_lazy_scratch_per_cta(bits);
+    return QSRTB_OK;
+}
+
 namespace {
 
 int check_common(int bits, int tailbite_context, int variant, int64_t n_tiles)

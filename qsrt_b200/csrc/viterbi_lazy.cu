@@ -2,23 +2,24 @@
 //
 // Same search, same results as viterbi.cu (and therefore as the reference kernels
 //   qsrt/csrc/qsrt_quantize_tiles_kernel.cuh:26-500 and qsrt_quantize_tiles_k2_kernel.cuh:47-366),
-// organised so that the constrained pass - half of all trellis steps - carries no
-// compare / select / position bookkeeping at all:
-//   * the constrained pass only takes minima and streams the step's path costs (one half per
-//     state) to a scratch slice in global memory;
-//   * the traceback needs the decision of ONE out-edge per step.  It recomputes that decision
+// organised so that the trellis steps carry no compare / select / position bookkeeping:
+//   * a pass only takes minima and streams the step's path costs (one half per state) to a
+//     scratch row in global memory;
+//   * a traceback needs the decision of ONE out-edge per step.  It recomputes that decision
 //     from the costs of the step before with exactly the arithmetic of the forward pass (same
 //     fp16 subtract / fused multiply-add / clamp, lowest predecessor on ties), so a traceback
-//     is a chain of 256 dependent links, each a handful of 2-byte reads;
-//   * a chain is latency-bound, so it is not run on its own: warp 0 advances the chain of the
-//     PREVIOUS tile by one link every second trellis step of the CURRENT tile (cp.async into
-//     shared memory, consumed two steps later), which hides the memory latency completely.
-//     Two scratch slots per CTA alternate between consecutive tiles;
-//   * the primer pass (its recorded half is a quarter of all steps) keeps the survivor
-//     decisions and the batched traceback of viterbi.cu, because its result - the boundary
-//     state - is needed before the constrained pass of the same tile can start;
-//   * the last tile of a CTA records decisions in both passes, so no chain is left to be
-//     walked at the end of the launch with nothing to hide its latency behind.
+//     is a chain of dependent links, each a handful of 2-byte reads;
+//   * a chain is latency-bound (about a microsecond per link from HBM), so it never runs on its
+//     own: one warp advances it by a link every second trellis step of whatever pass the CTA is
+//     running (cp.async of the predecessors' cost words into shared memory, consumed two steps
+//     later).  Warp 0 walks the constrained pass's chain (256 links, writes the states), warp 1
+//     the primer's (C links, yields the boundary state);
+//   * a primer's boundary state is needed before the same tile's constrained pass can start, so
+//     a CTA interleaves its tiles: P(0) P(1) C(0) P(2) C(1) P(3) C(2) ...  The primer chain of
+//     tile x+1 is walked during C(x), the constrained chain of tile x during P(x+2) and C(x+1);
+//   * the constrained passes of a CTA's last two tiles keep survivor decisions and the batched
+//     traceback of viterbi.cu (nothing follows them to hide a chain behind), as does every pass
+//     of a tile that met the fp16 clamp and is re-encoded with the literal arithmetic.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -34,37 +35,47 @@ namespace {
 using namespace qsrtb_vit;
 
 constexpr int kChainCadence = 2;  // trellis steps between two links of a chain (even: see run_pass)
-constexpr int kChainWarp = 0;      // the warp that walks the chain (any does equally well)
+constexpr int kNever = 0x7fffffff;
+constexpr int kInFlight = 3;      // tiles of a CTA whose input and states are live at a time
+constexpr int kPrimerRows = 130;  // cost rows of a primer buffer (C + 1 used, C <= 128)
 
-// The traceback in flight: the constrained pass of tile `tile`, whose cost rows are in `slot`.
-// `head` is what a link needs and changes with every link; warp 0 reads and writes it with one
-// 16-byte access.
+enum ChainKind { CHAIN_CONSTRAINED = 0, CHAIN_PRIMER = 1 };
+
+// A traceback in flight.  `head` is what a link needs and changes with every link; the walking
+// warp reads and writes it with one 16-byte access.
 struct ChainHead {
-    int ri;      // row whose decision is resolved next, 255 down to 0; -1 when no link is pending
-    int edge;    // trellis state after row ri
-    int slot;
-    int w_bits;  // the tile's rounded input at row ri (half bits)
+    int ri;      // symbol whose decision is resolved next, counting down; -1 when none is pending
+    int edge;    // trellis state after that symbol
+    int slot;    // which of the in-flight tiles (input, states)
+    int w_bits;  // the tile's rounded input at symbol ri (half bits)
 };
 struct Chain {
     ChainHead head;
-    int state;      // 0 none, 1 walking, 2 walked (states complete, outputs not yet written)
-    int pre_state;  // start (= end) state of the constrained pass
+    const uint8_t* rows;  // the pass's cost rows; the link at ri reads row ri + row_bias
+    int row_bias;         // -1 constrained (costs after symbol ri - 1), 0 primer (rows start one step early)
+    int state;            // 0 none, 1 walking, 2 walked
+    int pre_state;        // constrained: start (= end) state of the pass
+    int result;           // the state before symbol 0, once walked (the primer's boundary state)
     long long tile;
-    uint32_t cost_word[16];   // per predecessor: the 4-byte word holding its cost
+    uint32_t cost_word[16];  // per predecessor: the 4-byte word holding its cost
+};
+
+struct TileSlot {
+    int end_state;  // boundary state from the primer
+    int done;       // the tile was finished out of turn (re-encoded after meeting the clamp)
 };
 
 struct LazySmem {
-    __half in_h[2][256];
-    uint16_t states[2][256];
+    __half in_h[kInFlight][256];
+    uint16_t states[kInFlight][256];
     uint32_t red[32];
     __half warp_mins[2][32];
     __half shift[2];
     int edge;
     int pad;
-    __align__(16) Chain chain;
+    TileSlot slot[kInFlight];
+    __align__(16) Chain chain[2];  // [CHAIN_CONSTRAINED] walked by warp 0, [CHAIN_PRIMER] by warp 1
 };
-
-constexpr int kNever = 0x7fffffff;
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
 {
@@ -80,37 +91,35 @@ __device__ __forceinline__ __half e4m3_to_half(uint32_t b)
     return __half(raw);
 }
 
-// Issue the reads the link at (ri, e) needs: the cost of every predecessor k of out-edge e after
-// row ri - 1 (row 0 has no predecessors' costs).  The branch labels come from the copy of the
-// state table in shared memory.  Warp 0 only.
+// Issue the reads a link at out-edge e needs: the cost of every predecessor k of e in cost row
+// `row` (none for a constrained pass's symbol 0, row -1).  The branch labels come from the copy
+// of the state table in shared memory.  The chain's warp only.
 template <int K>
-__device__ __forceinline__ void chain_issue(Chain* ch, int ri, int e, const uint8_t* cost_rows, int lane)
+__device__ __forceinline__ void chain_issue(Chain* ch, int row, int e, int lane)
 {
     using G = Geo<K>;
-    if (lane < G::NK) {
-        if (ri > 0) {
-            const int pred = (e >> K) + lane * G::pred_stride;
-            cp_async4(&ch->cost_word[lane], cost_rows + (size_t(ri - 1) * G::edges + (pred & ~1)) * 2);
-        }
+    if (lane < G::NK && row >= 0) {
+        const int pred = (e >> K) + lane * G::pred_stride;
+        cp_async4(&ch->cost_word[lane], ch->rows + (size_t(row) * G::edges + (pred & ~1)) * 2);
     }
     cp_async_commit();
 }
 
 // Resolve the pending link and issue the reads of the next.  The decision is recomputed exactly
-// as acs_step computes the branch metrics of that row (same fp16 operations, same clamp), and
+// as acs_step computes the branch metrics of that step (same fp16 operations, same clamp), and
 // the lowest predecessor among the minima wins, as in the forward tournament.  Everything the
-// link needs sits at fixed shared-memory addresses, so its loads go out together.  Warp 0
-// only, after the link's reads have landed.  Returns false when no link was pending.
-template <int K, int MODE>
-__device__ __forceinline__ bool chain_link(Chain* ch, LazySmem* sm, const uint8_t* slot_base,
-                                           size_t slot_bytes, const uint8_t* labels, int lane)
+// link needs sits at fixed shared-memory addresses, so its loads go out together.  The chain's
+// warp only, after the link's reads have landed.  Returns false when no link was pending.
+template <int K, int MODE, int KIND>
+__device__ __forceinline__ bool chain_link(Chain* ch, LazySmem* sm, const uint8_t* labels, int lane)
 {
     using G = Geo<K>;
     cp_async_wait_all();
     const int4 h = *reinterpret_cast<const int4*>(&ch->head);
-    const uint32_t label = labels[((lane & (G::NK - 1)) << G::Kr) | h.y];
+    const uint32_t label = labels[((lane & (G::NK - 1)) << G::Kr) | (h.y & (G::edges - 1))];
     const uint32_t cw = ch->cost_word[lane & 15];
     const int pre_state = ch->pre_state;
+    const int row_bias = ch->row_bias;
     const int ri = h.x, e = h.y, slot = h.z;
     if (ri < 0) return false;
     uint32_t key = 0xffffffffu;
@@ -119,15 +128,15 @@ __device__ __forceinline__ bool chain_link(Chain* ch, LazySmem* sm, const uint8_
         const int pred = (e >> K) + lane * G::pred_stride;
         const __half inf = __ushort_as_half(0x7c00), top = __ushort_as_half(0x7bff);
         __half v;
-        if (ri == 0) {
+        if (KIND == CHAIN_CONSTRAINED && ri == 0) {
             v = __hmul(dh, dh);
             if constexpr (MODE != MODE_K2) v = __hmin(v, top);
             if (pred != pre_state) v = inf;
         } else {
             const uint32_t pbits = (pred & 1) ? (cw >> 16) : (cw & 0xffffu);
             v = __hfma(dh, dh, __ushort_as_half(static_cast<unsigned short>(pbits)));
-            if constexpr (MODE == MODE_FAST) {
-                if (ri < kSafeSteps) {  // these rows ran the clamped arithmetic
+            if constexpr (MODE == MODE_FAST && KIND == CHAIN_CONSTRAINED) {
+                if (ri < kSafeSteps) {  // these steps ran the clamped arithmetic
                     v = __hmin(v, top);
                     if (pbits == 0x7c00u) v = inf;
                 }
@@ -139,25 +148,47 @@ __device__ __forceinline__ bool chain_link(Chain* ch, LazySmem* sm, const uint8_
     const int decision = int(key & 31u);
     const int prev = (decision << (16 - 2 * K)) | (e >> K);
     const int next = ri - 1;
-    if (next >= 0) chain_issue<K>(ch, next, prev, slot_base + size_t(slot) * slot_bytes, lane);
+    if (next >= 0) chain_issue<K>(ch, next + row_bias, prev, lane);
     if (lane == 0) {
-        sm->states[slot][ri] = uint16_t((prev << K) | e);
+        if constexpr (KIND == CHAIN_CONSTRAINED) sm->states[slot][ri] = uint16_t((prev << K) | e);
         const int w_bits = next >= 0 ? int(__half_as_ushort(sm->in_h[slot][next])) : 0;
         *reinterpret_cast<int4*>(&ch->head) = make_int4(next, prev, slot, w_bits);
-        if (next < 0) ch->state = 2;
+        if (next < 0) {
+            ch->result = prev;
+            ch->state = 2;
+        }
     }
     __syncwarp();
     return true;
 }
 
-// Walk what is left of the chain without anything to hide the latency behind (at most 256
-// links; normally none are left).  Warp 0 only.
-template <int K, int MODE>
-__device__ __forceinline__ void chain_drain(Chain* ch, LazySmem* sm, const uint8_t* slot_base,
-                                            size_t slot_bytes, const uint8_t* labels, int lane)
+// Walk what is left of a chain without anything to hide the latency behind (normally nothing
+// is left).  The chain's warp only.
+template <int K, int MODE, int KIND>
+__device__ __forceinline__ void chain_drain(Chain* ch, LazySmem* sm, const uint8_t* labels, int lane)
 {
     for (int guard = 0; guard < 257; ++guard)
-        if (!chain_link<K, MODE>(ch, sm, slot_base, slot_bytes, labels, lane)) break;
+        if (!chain_link<K, MODE, KIND>(ch, sm, labels, lane)) break;
+}
+
+// Start a chain at (ri, edge) of the tile in `slot`.  All lanes of the chain's warp.
+template <int K>
+__device__ __forceinline__ void chain_start(Chain* ch, LazySmem* sm, const uint8_t* rows, int row_bias,
+                                            int ri, int edge, int slot, int pre_state, long long tile,
+                                            int lane)
+{
+    if (lane == 0) {
+        ch->rows = rows;
+        ch->row_bias = row_bias;
+        ch->state = 1;
+        ch->pre_state = pre_state;
+        ch->result = -1;
+        ch->tile = tile;
+        *reinterpret_cast<int4*>(&ch->head) =
+            make_int4(ri, edge, slot, int(__half_as_ushort(sm->in_h[slot][ri])));
+    }
+    __syncwarp();
+    chain_issue<K>(ch, ri + row_bias, edge, lane);
 }
 
 // Where thread t (< 256) finds its value of `tile` and where the results go (see TileIO).
@@ -229,31 +260,30 @@ __device__ __forceinline__ void store_tile(const TileIO& io, int64_t tile, const
     }
 }
 
-// Everything a tile's encode needs besides its labels.
+// Everything the passes of a CTA need besides the labels.
 struct LazyCtx {
     LazySmem* sm;
     __half* cost0;
     __half* cost1;
-    uint8_t* slot_base;   // this CTA's two scratch slots
-    size_t slot_bytes;
+    uint8_t* scratch;       // this CTA's cost rows: two constrained buffers, then two primer buffers
     const uint8_t* lut_state;
-    const uint8_t* labels;  // the 65,536 state-indexed labels in shared memory (for the chain)
+    const uint8_t* labels;  // the 65,536 state-indexed labels in shared memory (for the chains)
     const TileIO* io;
     int context;
-    int tick;             // trellis steps executed by this CTA so far
-    int chain_due;        // step at which warp 0 resolves the chain's next link (kNever: none)
+    int tick;               // trellis steps executed by this CTA so far
+    int chain_due;          // step at which this warp resolves its chain's next link (kNever: none)
 };
 
-// Finish the chain in flight, if any: walk its remaining links, then write its tile's results.
-// Called by all threads at a point where they are converged.
+// Finish the constrained chain in flight, if any: walk its remaining links, then write its
+// tile's results.  Called by all threads at a point where they are converged.
 template <int K, int CHAIN_MODE>
-__device__ __forceinline__ void chain_finish(LazyCtx& cx)
+__device__ __forceinline__ void finish_constrained_chain(LazyCtx& cx)
 {
-    Chain* ch = &cx.sm->chain;
+    Chain* ch = &cx.sm->chain[CHAIN_CONSTRAINED];
     __syncthreads();
     if (ch->state == 0) return;
-    if ((threadIdx.x >> 5) == kChainWarp)
-        chain_drain<K, CHAIN_MODE>(ch, cx.sm, cx.slot_base, cx.slot_bytes, cx.labels, threadIdx.x & 31);
+    if ((threadIdx.x >> 5) == CHAIN_CONSTRAINED)
+        chain_drain<K, CHAIN_MODE, CHAIN_CONSTRAINED>(ch, cx.sm, cx.labels, threadIdx.x & 31);
     __syncthreads();
     store_tile(*cx.io, ch->tile, cx.sm->states[ch->head.slot], cx.lut_state);
     __syncthreads();
@@ -261,26 +291,42 @@ __device__ __forceinline__ void chain_finish(LazyCtx& cx)
     __syncthreads();
 }
 
-// Encode the tile whose rounded input is in sm->in_h[slot].
-// Returns 0: invalid (MODE_FAST met the clamp; encode again with MODE_SAFE),
-//         1: sm->states[slot] holds the result,
-//         2: the result is being walked by the chain (lazy constrained pass).
-template <int K, int MODE, int UNITS, int NL>
-__device__ __forceinline__ int encode_tile_lazy(const uint32_t (&L)[UNITS][NL], LazyCtx& cx, int slot,
-                                                bool lazy, int64_t tile)
+// Finish the primer chain in flight, if any, and file its boundary state with its tile.
+template <int K, int CHAIN_MODE>
+__device__ __forceinline__ void finish_primer_chain(LazyCtx& cx)
+{
+    Chain* ch = &cx.sm->chain[CHAIN_PRIMER];
+    __syncthreads();
+    if (ch->state == 0) return;
+    if ((threadIdx.x >> 5) == CHAIN_PRIMER)
+        chain_drain<K, CHAIN_MODE, CHAIN_PRIMER>(ch, cx.sm, cx.labels, threadIdx.x & 31);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        cx.sm->slot[ch->head.slot].end_state = ch->result;
+        ch->state = 0;
+    }
+    __syncthreads();
+}
+
+// One pass over `steps` symbols of the tile in `slot`, starting at symbol `roll`.
+//   CONSTRAINED : the pass starts from (and must return to) pre_state;
+//   COSTS       : recorded steps store their path costs instead of survivor decisions;
+//   recorded steps are those from `record_from` on; their row is `row_of(i, ri)`.
+// Returns (block-uniform) whether MODE_FAST met the clamp.
+template <int K, int MODE, int UNITS, int NL, bool CONSTRAINED, bool COSTS>
+__device__ __forceinline__ bool run_pass(const uint32_t (&L)[UNITS][NL], LazyCtx& cx, int slot, int roll,
+                                         int steps, int pre_state, int record_from, uint8_t* rows,
+                                         int first_row_step, __half*& cur, __half*& inc)
 {
     using G = Geo<K>;
     constexpr int THREADS = kUnits / UNITS;
     constexpr int WARPS = THREADS / 32;
-    // Chains belong to tiles encoded lazily, i.e. with the fast or the dedicated K2 arithmetic;
-    // a tile being re-encoded with MODE_SAFE still advances a MODE_FAST chain.
+    // Chains belong to passes run with the fast or the dedicated K2 arithmetic; a tile being
+    // re-encoded with MODE_SAFE still advances MODE_FAST chains.
     constexpr int CHAIN_MODE = MODE == MODE_K2 ? MODE_K2 : MODE_FAST;
+    constexpr int row_stride = COSTS ? G::edges * 2 : G::row_bytes;
     LazySmem* sm = cx.sm;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int context = cx.context;
-    __half* cur = cx.cost0;
-    __half* inc = cx.cost1;
-    uint8_t* slot_rows = cx.slot_base + size_t(slot) * cx.slot_bytes;  // decision rows and cost rows alias
     __half2 track_max = u2h2(0u);
 
     // lag-2 renormalisation of the dedicated K2 arithmetic (k2 cuh:117-137, 211-230)
@@ -308,127 +354,115 @@ __device__ __forceinline__ int encode_tile_lazy(const uint32_t (&L)[UNITS][NL], 
     UNIT_LOOP(acs_step<K, M, FIRST, CONS, REC, NL, COSTS>(L[uu], int(threadIdx.x) + uu * THREADS, inc, \
                                                           cur, w, pre_state, shift2, row, TRACK))
 
-    auto run_pass = [&](int roll, int steps, int pre_state, int trace_start, auto constrained_tag,
-                        auto costs_tag) {
-        constexpr bool CONSTRAINED = decltype(constrained_tag)::value;
-        constexpr bool COSTS = decltype(costs_tag)::value;
-        constexpr int row_stride = COSTS ? G::edges * 2 : G::row_bytes;
+    if constexpr (MODE == MODE_K2) {
+        if (threadIdx.x == 0) {
+            sm->shift[0] = __ushort_as_half(0);
+            sm->shift[1] = __ushort_as_half(0);
+        }
+        __syncthreads();
+    }
+    // Every pass has an even number of steps, so the step counter is even after the second step
+    // of each pair below: the chains, whose links fall due on even counts, are looked at there.
+    auto step = [&](const int i, auto chain_tag) {
+        const int ri = (i + roll) & 255;
+        ++cx.tick;
+        if constexpr (decltype(chain_tag)::value) {
+            if (cx.tick == cx.chain_due) {  // kNever in every warp but the two that walk chains
+                bool more;
+                if (warp == CHAIN_CONSTRAINED)
+                    more = chain_link<K, CHAIN_MODE, CHAIN_CONSTRAINED>(&sm->chain[CHAIN_CONSTRAINED], sm,
+                                                                        cx.labels, lane);
+                else
+                    more = chain_link<K, CHAIN_MODE, CHAIN_PRIMER>(&sm->chain[CHAIN_PRIMER], sm, cx.labels,
+                                                                   lane);
+                cx.chain_due = more ? cx.tick + kChainCadence : kNever;
+            }
+        }
+        __half* t = cur; cur = inc; inc = t;
+        const __half w = sm->in_h[slot][ri];
+        // a recorded step's row: by symbol for decisions and constrained costs, by step for a
+        // primer's costs (which start one step before the first recorded decision)
+        uint8_t* row = rows + size_t(COSTS && !CONSTRAINED ? i - first_row_step : ri) * row_stride;
+        __half2 shift2 = u2h2(0u);
+        __half2 step_min2 = u2h2(kInf2);
         if constexpr (MODE == MODE_K2) {
-            if (threadIdx.x == 0) {
-                sm->shift[0] = __ushort_as_half(0);
-                sm->shift[1] = __ushort_as_half(0);
-            }
-            __syncthreads();
+            if (i > 0) k2_fold(i);
+            shift2 = __half2half2(sm->shift[i & 1]);
         }
-        // Every pass has an even number of steps, so the step counter is even after the second
-        // step of each pair below: the chain, whose links fall due on even counts, is looked at
-        // there only.
-        auto step = [&](const int i, auto chain_tag) {
-            const int ri = (i + roll) & 255;
-            ++cx.tick;
-            if constexpr (decltype(chain_tag)::value) {
-                if (cx.tick == cx.chain_due) {  // kNever in every warp but the chain's
-                    const bool more = chain_link<K, CHAIN_MODE>(&sm->chain, sm, cx.slot_base, cx.slot_bytes,
-                                                                cx.labels, lane);
-                    cx.chain_due = more ? cx.tick + kChainCadence : kNever;
-                }
-            }
-            __half* t = cur; cur = inc; inc = t;
-            const __half w = sm->in_h[slot][ri];
-            uint8_t* row = slot_rows + size_t(ri) * row_stride;
-            __half2 shift2 = u2h2(0u);
-            __half2 step_min2 = u2h2(kInf2);
+        if (i == 0) {
+            if constexpr (MODE == MODE_K2)
+                ACS(MODE, true, CONSTRAINED, CONSTRAINED, step_min2);
+            else if constexpr (MODE == MODE_FAST && CONSTRAINED)
+                ACS(MODE_SAFE, true, true, true, track_max);
+            else
+                ACS(MODE, true, CONSTRAINED, CONSTRAINED, track_max);
+        } else if (i < record_from) {
+            if constexpr (MODE == MODE_K2)
+                ACS(MODE, false, false, false, step_min2);
+            else
+                ACS(MODE, false, false, false, track_max);
+        } else {
             if constexpr (MODE == MODE_K2) {
-                if (i > 0) k2_fold(i);
-                shift2 = __half2half2(sm->shift[i & 1]);
-            }
-            if (i == 0) {
-                if constexpr (MODE == MODE_K2)
-                    ACS(MODE, true, CONSTRAINED, CONSTRAINED, step_min2);
-                else if constexpr (MODE == MODE_FAST && CONSTRAINED)
-                    ACS(MODE_SAFE, true, true, true, track_max);
+                ACS(MODE, false, false, true, step_min2);
+            } else if constexpr (MODE == MODE_FAST && CONSTRAINED) {
+                if (i < kSafeSteps)  // unreachable states exist for the first few constrained steps
+                    ACS(MODE_SAFE, false, false, true, track_max);
                 else
-                    ACS(MODE, true, CONSTRAINED, CONSTRAINED, track_max);
-            } else if (i < trace_start) {
-                if constexpr (MODE == MODE_K2)
-                    ACS(MODE, false, false, false, step_min2);
-                else
-                    ACS(MODE, false, false, false, track_max);
-            } else {
-                if constexpr (MODE == MODE_K2) {
-                    ACS(MODE, false, false, true, step_min2);
-                } else if constexpr (MODE == MODE_FAST && CONSTRAINED) {
-                    if (i < kSafeSteps)  // unreachable states exist for the first few constrained steps
-                        ACS(MODE_SAFE, false, false, true, track_max);
-                    else
-                        ACS(MODE, false, false, true, track_max);
-                } else {
                     ACS(MODE, false, false, true, track_max);
-                }
+            } else {
+                ACS(MODE, false, false, true, track_max);
             }
-            if constexpr (MODE == MODE_K2) k2_publish(i, step_min2);
-            __syncthreads();
-        };
-        for (int i = 0; i < steps; i += 2) {
-            step(i, std::false_type{});
-            step(i + 1, std::true_type{});
         }
+        if constexpr (MODE == MODE_K2) k2_publish(i, step_min2);
+        __syncthreads();
     };
-    auto clamp_met = [&]() {
+    for (int i = 0; i < steps; i += 2) {
+        step(i, std::false_type{});
+        step(i + 1, std::true_type{});
+    }
+#undef ACS
+#undef UNIT_LOOP
+    if constexpr (MODE == MODE_FAST) {
         const bool over = !(__hlt(__low2half(track_max), u2h2(kMax2).x) &&
                             __hlt(__high2half(track_max), u2h2(kMax2).x));
         return __syncthreads_or(over) != 0;
-    };
-
-    // Primer: 2*C symbols centred on symbol 0, decisions kept for the last C of them.
-    run_pass(256 - context, 2 * context, -1, context, std::false_type{}, std::false_type{});
-    if constexpr (MODE == MODE_FAST) {
-        if (clamp_met()) return 0;
     }
+    return false;
+}
+
+// Encode the tile in `slot` from scratch with survivor decisions in both passes and the batched
+// traceback (the organisation of viterbi.cu); `rows` is a scratch area no chain is reading.
+// Leaves the states in sm->states[slot].  Returns false if MODE_FAST met the clamp.
+template <int K, int MODE, int UNITS, int NL>
+__device__ __forceinline__ bool encode_with_decisions(const uint32_t (&L)[UNITS][NL], LazyCtx& cx, int slot,
+                                                      uint8_t* rows)
+{
+    LazySmem* sm = cx.sm;
+    const int context = cx.context;
+    __half* cur = cx.cost0;
+    __half* inc = cx.cost1;
+    if (run_pass<K, MODE, UNITS, NL, false, false>(L, cx, slot, 256 - context, 2 * context, -1, context, rows,
+                                                   0, cur, inc))
+        return false;
     int boundary;
     if constexpr (MODE == MODE_K2)
-        boundary = boundary_argmin<K, false, UNITS>(cur, sm->red);  // final primer step (k2 cuh:282)
+        boundary = boundary_argmin<K, false, UNITS>(cur, sm->red);
     else
-        boundary = boundary_argmin<K, K != 2, UNITS>(inc, sm->red);  // step before the last (cuh:375,401)
-    const int end_state = traceback<K, UNITS>(slot_rows, reinterpret_cast<uint8_t*>(cx.cost0), context - 1,
+        boundary = boundary_argmin<K, K != 2, UNITS>(inc, sm->red);
+    const int end_state = traceback<K, UNITS>(rows, reinterpret_cast<uint8_t*>(cx.cost0), context - 1,
                                               boundary, false, sm->states[slot], &sm->edge);
-
-    // Constrained pass: starts from and must return to end_state.
-    if (lazy) {
-        run_pass(0, 256, end_state, 0, std::true_type{}, std::true_type{});
-        if constexpr (MODE == MODE_FAST) {
-            if (clamp_met()) return 0;
-        }
-        chain_finish<K, CHAIN_MODE>(cx);  // the previous tile's chain had this tile's 512 steps
-        Chain* ch = &sm->chain;
-        if (warp == kChainWarp) {
-            if (lane == 0) {
-                ch->state = 1;
-                ch->pre_state = end_state;
-                ch->tile = tile;
-                *reinterpret_cast<int4*>(&ch->head) =
-                    make_int4(255, end_state, slot, int(__half_as_ushort(sm->in_h[slot][255])));
-            }
-            __syncwarp();
-            chain_issue<K>(ch, 255, end_state, slot_rows, lane);
-        }
-        cx.chain_due = warp == kChainWarp ? cx.tick + kChainCadence : kNever;
-        __syncthreads();
-        return 2;
-    }
-    run_pass(0, 256, end_state, 0, std::true_type{}, std::false_type{});
-    if constexpr (MODE == MODE_FAST) {
-        if (clamp_met()) return 0;
-    }
-    traceback<K, UNITS>(slot_rows, reinterpret_cast<uint8_t*>(cx.cost0), 255, end_state, true,
-                        sm->states[slot], &sm->edge);
-    return 1;
-#undef ACS
-#undef UNIT_LOOP
+    if (run_pass<K, MODE, UNITS, NL, true, false>(L, cx, slot, 0, 256, end_state, 0, rows, 0, cur, inc))
+        return false;
+    traceback<K, UNITS>(rows, reinterpret_cast<uint8_t*>(cx.cost0), 255, end_state, true, sm->states[slot],
+                        &sm->edge);
+    return true;
 }
 
 template <int K>
-constexpr size_t lazy_slot_bytes() { return size_t(256) * Geo<K>::edges * 2; }
+constexpr size_t lazy_cta_bytes()
+{
+    return size_t(2 * 256 + 2 * kPrimerRows) * Geo<K>::edges * 2;  // two constrained and two primer buffers
+}
 
 template <int K, bool DEDICATED, int UNITS>
 __global__ void __launch_bounds__(kUnits / UNITS, 1)
@@ -437,30 +471,34 @@ viterbi_lazy_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
                     int context)
 {
     using G = Geo<K>;
+    constexpr int THREADS = kUnits / UNITS;
+    constexpr int NL = UNITS >= 2 ? 32 : 16;
+    constexpr int MODE = DEDICATED ? MODE_K2 : MODE_FAST;  // arithmetic of every pass but re-encodes
     extern __shared__ __align__(16) uint8_t smem_raw[];
     LazyCtx cx;
     cx.cost0 = reinterpret_cast<__half*>(smem_raw);
     cx.cost1 = cx.cost0 + G::edges;
     cx.sm = reinterpret_cast<LazySmem*>(smem_raw + 2 * G::edges * sizeof(__half));
+    LazySmem* sm = cx.sm;
     uint8_t* labels = smem_raw + 2 * G::edges * sizeof(__half) + sizeof(LazySmem);
     for (int i = threadIdx.x; i < 65536 / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(labels)[i] = reinterpret_cast<const uint4*>(lut_state)[i];
     cx.labels = labels;
-    cx.slot_bytes = lazy_slot_bytes<K>();
-    cx.slot_base = scratch_base + size_t(blockIdx.x) * 2 * cx.slot_bytes;
+    cx.scratch = scratch_base + size_t(blockIdx.x) * lazy_cta_bytes<K>();
+    // buffers alternate between consecutive tiles
+    auto constrained_rows = [&](int x) { return cx.scratch + size_t((x & 1) * 256) * (G::edges * 2); };
+    auto primer_rows = [&](int x) { return cx.scratch + size_t(512 + (x & 1) * kPrimerRows) * (G::edges * 2); };
     cx.lut_state = lut_state;
     cx.io = &io;
     cx.context = context;
     cx.tick = 0;
     cx.chain_due = kNever;
-    if (threadIdx.x == 0) {
-        cx.sm->chain.state = 0;
-        cx.sm->chain.head.ri = -1;
+    if (threadIdx.x < 2) {
+        sm->chain[threadIdx.x].state = 0;
+        sm->chain[threadIdx.x].head.ri = -1;
+        sm->chain[threadIdx.x].head.edge = 0;
     }
 
-    constexpr int THREADS = kUnits / UNITS;
-    constexpr int NL = UNITS >= 2 ? 32 : 16;
-    constexpr int CHAIN_MODE = DEDICATED ? MODE_K2 : MODE_FAST;
     uint32_t L[UNITS][NL];
 #pragma unroll
     for (int uu = 0; uu < UNITS; ++uu) {
@@ -482,25 +520,121 @@ viterbi_lazy_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
     }
     __syncthreads();
 
-    int slot = 0;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, slot ^= 1) {
-        const bool last = tile + gridDim.x >= n_tiles;
-        // the slot's rows, input and states may still belong to a chain (after a tile that
-        // started none): finish it before they are overwritten
-        if (cx.sm->chain.state != 0 && cx.sm->chain.head.slot == slot) chain_finish<K, CHAIN_MODE>(cx);
-        load_tile<DEDICATED>(io, tile, cx.sm->in_h[slot]);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int count = int((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);  // this CTA's tiles
+    auto tile_of = [&](int x) { return int64_t(blockIdx.x) + int64_t(x) * gridDim.x; };
+    // A primer's chain needs a pass to ride on before its tile's constrained pass: with a single
+    // tile there is none.  (With a one-symbol context the primer's first step would have to be
+    // a recorded one; that case keeps decisions too.)
+    const bool lazy_primers = count >= 2 && context >= 2;
+
+    // Re-encode tile x with the literal arithmetic, out of turn, and write its results.
+    auto reencode = [&](int x) {
+        const int slot = x % kInFlight;
+        // the primer buffer of x is free: its primer was just abandoned, or its chain is finished
+        encode_with_decisions<K, MODE_SAFE, UNITS, NL>(L, cx, slot, primer_rows(x));
+        store_tile(io, tile_of(x), sm->states[slot], lut_state);
+        if (threadIdx.x == 0) sm->slot[slot].done = 1;
         __syncthreads();
-        int result;
-        if constexpr (DEDICATED) {
-            result = encode_tile_lazy<K, MODE_K2, UNITS, NL>(L, cx, slot, !last, tile);
+    };
+
+    // P(x): load tile x and run its primer; leaves its boundary state with the slot, or starts
+    // the primer chain that will.  Returns x if the tile met the clamp and has to be re-encoded,
+    // else -1.
+    auto primer = [&](int x) -> int {
+        const int slot = x % kInFlight;
+        // the slot's input and states may still belong to the constrained chain of tile x - 3
+        if (sm->chain[CHAIN_CONSTRAINED].state != 0 && sm->chain[CHAIN_CONSTRAINED].head.slot == slot)
+            finish_constrained_chain<K, MODE>(cx);
+        load_tile<DEDICATED>(io, tile_of(x), sm->in_h[slot]);
+        if (threadIdx.x == 0) sm->slot[slot].done = 0;
+        __syncthreads();
+        __half* cur = cx.cost0;
+        __half* inc = cx.cost1;
+        uint8_t* rows = primer_rows(x);
+        bool over;
+        if (lazy_primers)
+            over = run_pass<K, MODE, UNITS, NL, false, true>(L, cx, slot, 256 - context, 2 * context, -1,
+                                                             context - 1, rows, context - 1, cur, inc);
+        else
+            over = run_pass<K, MODE, UNITS, NL, false, false>(L, cx, slot, 256 - context, 2 * context, -1,
+                                                              context, rows, 0, cur, inc);
+        if (over) return x;  // MODE_FAST only
+        int boundary;
+        if constexpr (MODE == MODE_K2)
+            boundary = boundary_argmin<K, false, UNITS>(cur, sm->red);  // final primer step (k2 cuh:282)
+        else
+            boundary = boundary_argmin<K, K != 2, UNITS>(inc, sm->red);  // step before the last (cuh:375,401)
+        if (lazy_primers) {
+            finish_primer_chain<K, MODE>(cx);  // tile x - 1's: it had a constrained pass and this primer
+            if (warp == CHAIN_PRIMER)
+                chain_start<K>(&sm->chain[CHAIN_PRIMER], sm, rows, 0, context - 1, boundary, slot, -1,
+                               tile_of(x), lane);
+            cx.chain_due = warp == CHAIN_PRIMER ? cx.tick + kChainCadence
+                           : warp == CHAIN_CONSTRAINED ? cx.chain_due : kNever;
+            __syncthreads();
         } else {
-            result = encode_tile_lazy<K, MODE_FAST, UNITS, NL>(L, cx, slot, !last, tile);
-            if (result == 0) result = encode_tile_lazy<K, MODE_SAFE, UNITS, NL>(L, cx, slot, false, tile);
+            const int end_state = traceback<K, UNITS>(rows, reinterpret_cast<uint8_t*>(cx.cost0), context - 1,
+                                                      boundary, false, sm->states[slot], &sm->edge);
+            if (threadIdx.x == 0) sm->slot[slot].end_state = end_state;
+            __syncthreads();
         }
-        if (result == 1) store_tile(io, tile, cx.sm->states[slot], lut_state);
-        __syncthreads();
+        return -1;
+    };
+
+    // C(x): the constrained pass of tile x, with path costs and a chain if two more passes
+    // follow to walk it during, else with survivor decisions.  Returns x if the tile met the
+    // clamp and has to be re-encoded, else -1.
+    auto constrained = [&](int x) -> int {
+        const int slot = x % kInFlight;
+        if (sm->slot[slot].done) return -1;
+        if (sm->chain[CHAIN_PRIMER].state != 0 && sm->chain[CHAIN_PRIMER].head.slot == slot)
+            finish_primer_chain<K, MODE>(cx);
+        const int end_state = sm->slot[slot].end_state;
+        const bool lazy = x + 2 < count;
+        uint8_t* rows = constrained_rows(x);
+        __half* cur = cx.cost0;
+        __half* inc = cx.cost1;
+        // tile x - 2's chain read these rows; it is finished by the time tile x - 1's starts, but
+        // tile x - 1 may have started none
+        if (sm->chain[CHAIN_CONSTRAINED].state != 0 && sm->chain[CHAIN_CONSTRAINED].rows == rows)
+            finish_constrained_chain<K, MODE>(cx);
+        if (lazy) {
+            if (run_pass<K, MODE, UNITS, NL, true, true>(L, cx, slot, 0, 256, end_state, 0, rows, 0, cur, inc))
+                return x;
+            finish_constrained_chain<K, MODE>(cx);  // tile x - 1's: it had a primer and this pass
+            if (warp == CHAIN_CONSTRAINED)
+                chain_start<K>(&sm->chain[CHAIN_CONSTRAINED], sm, rows, -1, 255, end_state, slot, end_state,
+                               tile_of(x), lane);
+            cx.chain_due = warp == CHAIN_CONSTRAINED ? cx.tick + kChainCadence
+                           : warp == CHAIN_PRIMER ? cx.chain_due : kNever;
+            __syncthreads();
+        } else {
+            if (run_pass<K, MODE, UNITS, NL, true, false>(L, cx, slot, 0, 256, end_state, 0, rows, 0, cur, inc))
+                return x;
+            traceback<K, UNITS>(rows, reinterpret_cast<uint8_t*>(cx.cost0), 255, end_state, true,
+                                sm->states[slot], &sm->edge);
+            store_tile(io, tile_of(x), sm->states[slot], lut_state);
+            __syncthreads();
+        }
+        return -1;
+    };
+
+    // P(0) P(1) C(0) P(2) C(1) ... : every function above has exactly one call site, so that the
+    // labels stay in registers through all of them.
+#pragma unroll 1
+    for (int turn = 0; turn <= 2 * count; ++turn) {
+        int redo = -1;
+        if (turn == 0 || (turn & 1)) {
+            const int p = (turn + 1) >> 1;  // turns 0, 1, 3, 5, ...: the primers of tiles 0, 1, 2, 3, ...
+            if (p < count) redo = primer(p);
+        } else {
+            redo = constrained((turn >> 1) - 1);  // turns 2, 4, 6, ...: the constrained passes
+        }
+        if (redo >= 0) reencode(redo);
     }
-    chain_finish<K, CHAIN_MODE>(cx);
+    finish_constrained_chain<K, MODE>(cx);
+    finish_primer_chain<K, MODE>(cx);  // none is left unless its tile was finished out of turn
 }
 
 template <int K>
@@ -528,7 +662,8 @@ int launch_lazy(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, con
 
 size_t qsrtb_lazy_scratch_per_cta(int bits)
 {
-    return 2 * (size_t(256) << (16 - bits)) * 2;  // two slots of 256 rows of 2^(16-bits) halves
+    // two constrained buffers of 256 cost rows and two primer buffers, rows of 2^(16-bits) halves
+    return size_t(2 * 256 + 2 * kPrimerRows) * (size_t(2) << (16 - bits));
 }
 
 int qsrtb_lazy_launch(const qsrtb_vit::TileIO& io, int64_t n_tiles, const uint8_t* lut_state,

@@ -89,8 +89,8 @@ def prepared_table(codebook: torch.Tensor, bits: int, device: torch.device):
 def traceback_scratch(device: torch.device, bits: int, cost_rows: bool = False) -> torch.Tensor:
     """Traceback scratch of the current stream: one slice per resident CTA of the persistent
     grid.  Keyed by stream so that searches enqueued on different streams never share rows.
-    ``cost_rows`` asks for the two slots of path-cost rows per CTA that an explicit
-    ``traceback=2`` needs at every rate (the default size already has them at 3 and 4 bits)."""
+    ``cost_rows`` asks for the path-cost rows per CTA that an explicit ``traceback=2`` needs at
+    every rate (the default size already has them at 3 and 4 bits)."""
 
     key = (str(device), bits, torch.cuda.current_stream(device).cuda_stream, bool(cost_rows))
     buffer = _scratch.get(key)
@@ -103,8 +103,12 @@ def traceback_scratch(device: torch.device, bits: int, cost_rows: bool = False) 
             )
         size = wanted.value
         if cost_rows:
-            sms = torch.cuda.get_device_properties(device).multi_processor_count
-            size = max(size, sms * 2 * 256 * (2 << (16 - bits)))
+            with torch.cuda.device(device):
+                _lib.check(
+                    _lib.lib().qsrtb_viterbi_cost_scratch_bytes(bits, 1 << 30, ctypes.byref(wanted)),
+                    "qsrtb_viterbi_cost_scratch_bytes",
+                )
+            size = max(size, wanted.value)
         buffer = torch.empty(size, dtype=torch.uint8, device=device)
         _scratch[key] = buffer
     return buffer
