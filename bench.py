@@ -703,12 +703,12 @@ def cpu_baseline(payload, bits: int) -> dict:
 # ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
 SEARCH_KERNEL = {
     2: "viterbi_kernel<2, dedicated, 2 units/thread> (survivor decisions)",
-    3: "viterbi_lazy_kernel<3, generic, 2 units/thread> (path costs in the constrained pass)",
-    4: "viterbi_lazy_kernel<4, generic, 2 units/thread> (path costs in the constrained pass)",
+    3: "viterbi_lazy_kernel<3, generic, 2 units/thread> (path costs, decisions recomputed by the traceback chains)",
+    4: "viterbi_lazy_kernel<4, generic, 2 units/thread> (path costs, decisions recomputed by the traceback chains)",
 }
 NCU_DRAM_BYTES_PER_TILE = {
     2: (823.1e6 + 337.3e6) / 592,
-    3: (4906.3e6 + 412.0e6) / 1184,
+    3: (6528.9e6 + 500.5e6) / 1184,
     4: None,
 }
 NCU_DRAM_SOURCE = {
