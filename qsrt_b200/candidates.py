@@ -104,7 +104,8 @@ def _quantize_members(weights, product_cache, weights_q, err, encoded_q, row_beg
     _, size_k, size_n = weights.shape
     lut, lut_pm, abs_max = prepared_table(enc._codebook_for(quant_args, bits), bits, device)
     dedicated = bits == 2 and abs_max == abs_max and 0.0 < abs_max <= K2_DEDICATED_MAX_LABEL
-    scratch = traceback_scratch(device, bits)
+    variant, cost_rows = _tiles.search_variant(dedicated, quant_args)
+    scratch = traceback_scratch(device, bits, cost_rows=cost_rows)
     visited = columns.numel() if columns is not None else size_n // 16
     row_bytes = row_begin * size_n * 4
     with torch.cuda.device(device), _tiles.timed_search(device, count * visited, bits):
@@ -113,7 +114,7 @@ def _quantize_members(weights, product_cache, weights_q, err, encoded_q, row_beg
                 weights.data_ptr() + row_bytes, product_cache.data_ptr() + row_bytes, float(multiplier),
                 table.data_ptr(), count, size_n, size_n, size_n, size_k * size_n, size_k * size_n,
                 lut.data_ptr(), lut_pm.data_ptr(), bits, int(quant_args.get("tailbite_context", 128)),
-                1 if dedicated else 0, weights_q.data_ptr() + row_bytes, err.data_ptr() + row_bytes,
+                variant, weights_q.data_ptr() + row_bytes, err.data_ptr() + row_bytes,
                 encoded_q.data_ptr() + (row_begin // 16) * (size_n // 16) * 256 * 2,
                 (size_k // 16) * (size_n // 16) * 256,
                 columns.data_ptr() if columns is not None else None, visited if columns is not None else 0,

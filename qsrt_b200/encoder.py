@@ -608,7 +608,8 @@ def _quantize_rows(w_rows, comp_rows, multiplier, wq_rows, err_rows, states_row,
     device = w_rows.device
     lut, lut_pm, abs_max = prepared_table(_codebook_for(quant_args, bits), bits, device)
     dedicated = bits == 2 and abs_max == abs_max and 0.0 < abs_max <= K2_DEDICATED_MAX_LABEL
-    scratch = traceback_scratch(device, bits)
+    variant, cost_rows = _tiles.search_variant(dedicated, quant_args)
+    scratch = traceback_scratch(device, bits, cost_rows=cost_rows)
     visited = tile_map.numel() if tile_map is not None else n // 16
     with torch.cuda.device(device), _tiles.timed_search(device, batch * visited, bits):
         _lib.check(
@@ -616,7 +617,7 @@ def _quantize_rows(w_rows, comp_rows, multiplier, wq_rows, err_rows, states_row,
                 w_rows.data_ptr(), comp_rows.data_ptr() if comp_rows is not None else None,
                 float(multiplier), batch, n, ld, comp_ld, w_stride, comp_stride,
                 lut.data_ptr(), lut_pm.data_ptr(), bits, int(quant_args.get("tailbite_context", 128)),
-                1 if dedicated else 0, wq_rows.data_ptr(),
+                variant, wq_rows.data_ptr(),
                 err_rows.data_ptr() if err_rows is not None else None,
                 states_row.data_ptr(), state_stride,
                 tile_map.data_ptr() if tile_map is not None else None,

@@ -114,6 +114,20 @@ def traceback_scratch(device: torch.device, bits: int, cost_rows: bool = False) 
     return buffer
 
 
+def search_variant(dedicated: bool, quant_args: dict | None = None, units_per_thread: int = 0,
+                   traceback: int | None = None) -> tuple[int, bool]:
+    """The ``variant`` word of the search entry points and whether the launch needs the
+    path-cost scratch at every rate.  ``quant_args["tile_search_traceback"]`` (0 the kernel's
+    choice, 1 survivor decisions, 2 path costs) is this library's own tuning key; the results do
+    not depend on it."""
+
+    if traceback is None:
+        traceback = int((quant_args or {}).get("tile_search_traceback", 0))
+    if traceback not in (0, 1, 2):
+        raise ValueError("traceback must be 0 (kernel's choice), 1 (decisions) or 2 (path costs)")
+    return (1 if dedicated else 0) | (int(units_per_thread) << 4) | (traceback << 6), traceback == 2
+
+
 def encode_tiles(
     tiles: torch.Tensor,
     codebook: torch.Tensor,
@@ -142,8 +156,7 @@ def encode_tiles(
         raise ValueError("tailbite_context must be in 1..128")
     if units_per_thread not in (0, 1, 2):
         raise ValueError("units_per_thread must be 0 (per-rate default), 1 or 2")
-    if traceback not in (0, 1, 2):
-        raise ValueError("traceback must be 0 (kernel's choice), 1 (decisions) or 2 (path costs)")
+    variant, cost_rows = search_variant(False, None, units_per_thread, traceback)
     tiles = tiles.contiguous()
     device = tiles.device
     lut, lut_pm, abs_max = prepared_table(codebook, bits, device)
@@ -157,13 +170,12 @@ def encode_tiles(
     indices = torch.empty_like(tiles, dtype=torch.int16)
     if tiles.shape[0] == 0:
         return output, indices
-    scratch = traceback_scratch(device, bits, cost_rows=traceback == 2)
+    scratch = traceback_scratch(device, bits, cost_rows=cost_rows)
     with torch.cuda.device(device), timed_search(device, tiles.shape[0], bits):
         _lib.check(
             _lib.lib().qsrtb_quantize_tiles(
                 tiles.data_ptr(), tiles.shape[0], lut.data_ptr(), lut_pm.data_ptr(), bits,
-                int(tailbite_context), (1 if dedicated else 0) | (int(units_per_thread) << 4) | (int(traceback) << 6),
-                output.data_ptr(),
+                int(tailbite_context), variant | (1 if dedicated else 0), output.data_ptr(),
                 indices.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream_ptr(device),
             ),
             "qsrtb_quantize_tiles",

@@ -284,3 +284,34 @@ def test_quantize_qsrt_batch_against_reference_run(cuda_device, monkeypatch, nam
             want = float(golden[f"{key}_proxy"])
             assert abs(result["proxy"] - want) <= 2e-2 * want, key
     print(name, "tile identity per candidate:", identities)
+
+
+def test_traceback_organisations_agree_through_the_recursion(cuda_device):
+    """The whole BlockLDLQ recursion (rows read in place, compensation added in the kernel,
+    per-member source and owner, per-tile rate maps) with survivor decisions and with path costs:
+    same payload, same reconstruction.  Wide matrices so that every 16-row step gives the CTAs
+    several tiles each."""
+
+    g = torch.Generator().manual_seed(9)
+    wide = 4096
+    weights = torch.randn((3, 128, wide), generator=g).to(cuda_device)
+    Ls = torch.tril(0.05 * torch.randn((3, 128, 128), generator=g), diagonal=-1).to(cuda_device)
+    for bits in (3, 4):
+        outs = []
+        for organisation in (1, 2):
+            args = {"K": bits, "devices": [str(cuda_device)], "ldlq_tf32": False, "tailbite_context": 128,
+                    "buf_size_k": 128, "sqg_e4m3_luts_by_bits": LUTS, "tile_search_traceback": organisation}
+            outs.append(encoder.ldlq_batched(weights.clone(), Ls, args))
+        assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][0], outs[1][0])
+    rates = [3, 4] * (wide // 32)
+    members = []
+    for organisation in (1, 2):
+        members.append([_args(cuda_device, "n", rates, tile_search_traceback=organisation)] * 3)
+    kept = encoder.ldlq_mixed_batched(weights, Ls, members[0])
+    lazy = encoder.ldlq_mixed_batched(weights, Ls, members[1])
+    assert torch.equal(kept[1], lazy[1]) and torch.equal(kept[0], lazy[0])
+    index = torch.tensor([0, 0, 2], device=cuda_device)
+    kept = encoder.ldlq_mixed_batched(weights, Ls, members[0], source_indices=index)
+    lazy = encoder.ldlq_mixed_batched(weights, Ls, members[1], source_indices=index)
+    assert torch.equal(kept[1], lazy[1]) and torch.equal(kept[0], lazy[0])
+

@@ -139,6 +139,21 @@ def test_traceback_organisations_agree(cuda_device, bits, generic, context):
     assert torch.equal(chosen[1], kept[1])
 
 
+@pytest.mark.parametrize("extra", [1, 147, 148, 149, 296, 300])
+def test_interleaved_passes_at_every_tile_count(cuda_device, extra):
+    """The path-cost organisation interleaves the passes of a CTA's tiles (primer of the next
+    tile before the constrained pass of this one); CTAs with one, two, three and four tiles, and
+    launches where the CTAs differ in their count, all give the states of the decisions kernel."""
+
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    tiles = helpers.make_tiles("heavy", sms + extra, seed=extra).to(cuda_device)
+    for bits in (3, 4):
+        lut = _lut(bits)
+        kept = tile_api.encode_tiles(tiles, lut, bits, 128, traceback=1)
+        lazy = tile_api.encode_tiles(tiles, lut, bits, 128, traceback=2)
+        assert torch.equal(kept[1], lazy[1]) and torch.equal(kept[0], lazy[0])
+
+
 def test_lazy_traceback_matches_reference_kernel(cuda_device):
     """The path-cost organisation against the unmodified reference kernel, every family."""
 
