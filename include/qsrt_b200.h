@@ -55,8 +55,9 @@ int qsrtb_lut_prepare(const uint8_t* lut_state, int bits, uint8_t* lut_pm, float
  *
  * qsrtb_viterbi_scratch_bytes: bytes of traceback scratch wanted for `n_tiles` tiles on the
  * current device (a persistent grid is used, so this saturates at one slice per resident CTA:
- * 0.5 or 1 MiB of survivor decisions at 2 bits or when no CTA gets a second tile, else the
- * path-cost rows of qsrtb_viterbi_cost_scratch_bytes, 6 MiB at 4 bits and 12 MiB at 3).  A call given less scratch than
+ * 0.5 or 1 MiB of survivor decisions when no CTA gets a second tile, else path-cost rows: 6 MiB
+ * at 4 bits, 12 MiB at 3 and at 2 - where only the dedicated arithmetic uses them, storing
+ * every second row).  A call given less scratch than
  * that still works: it keeps survivor decisions for every step, on as many CTAs as the scratch
  * has slices.
  */
@@ -72,8 +73,9 @@ int qsrtb_viterbi_cost_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
  * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = path
  * costs, from which the tracebacks recompute the one decision per step they need while the
  * passes of the CTA's next tiles run - all passes but the constrained ones of a CTA's last two
- * tiles; 0 = 2 where it pays: 3 or 4 bits, tailbite_context 128, more tiles than SMs, scratch
- * as qsrtb_viterbi_scratch_bytes says; an explicit 2 needs qsrtb_viterbi_cost_scratch_bytes).
+ * tiles; 0 = 2 where it pays: 3 or 4 bits or the dedicated K2 arithmetic, tailbite_context 128,
+ * more tiles than SMs, scratch as qsrtb_viterbi_scratch_bytes says; an explicit 2 needs
+ * qsrtb_viterbi_cost_scratch_bytes).
  * Results are identical for every layout and organisation. */
 #define QSRTB_VARIANT_DEDICATED_K2 1
 #define QSRTB_VARIANT_LAYOUT(units) ((units) << 4)

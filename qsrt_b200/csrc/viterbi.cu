@@ -344,7 +344,7 @@ extern "C" int qsrtb_viterbi_scratch_bytes(int bits, int64_t n_tiles, size_t* by
     const size_t row_bytes = bits == 4 ? 2048 : 4096;
     // Launches that give a CTA more than one tile keep path costs instead of survivor decisions
     // for half of the steps (viterbi_lazy.cu), which takes two slots of 256 cost rows per CTA.
-    const size_t per_cta = (bits != 2 && n_tiles > sms) ? qsrtb_lazy_scratch_per_cta(bits) : 256 * row_bytes;
+    const size_t per_cta = n_tiles > sms ? qsrtb_lazy_scratch_per_cta(bits, 1) : 256 * row_bytes;
     *bytes = size_t(grid > 0 ? grid : 1) * per_cta;
     return QSRTB_OK;
 }
@@ -355,7 +355,7 @@ extern "C" int qsrtb_viterbi_cost_scratch_bytes(int bits, int64_t n_tiles, size_
     const int sms = resident_ctas();
     if (sms <= 0) return qsrtb_fail(QSRTB_ECUDA, "cannot query the device");
     const int64_t grid = n_tiles < sms ? n_tiles : sms;
-    *bytes = size_t(grid > 0 ? grid : 1) * qsrtb_lazy_scratch_per_cta(bits);
+    *bytes = size_t(grid > 0 ? grid : 1) * qsrtb_lazy_scratch_per_cta(bits, 0);
     return QSRTB_OK;
 }
 
@@ -400,17 +400,17 @@ int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const 
     const int layout = (variant >> 4) & 3;
     const int units = layout != 0 ? layout : (bits == 3 ? 1 : 2);
     // Traceback organisation (bits 6-7): 1 = survivor decisions for every recorded step, 2 = path
-    // costs for the constrained pass of all but a CTA's last tile (viterbi_lazy.cu), 0 = the
-    // latter where it pays: three or four bits (a K2 cost row is eight times its decision row,
-    // which costs more than the bookkeeping saves), full tail-biting context (the chain of one
-    // tile needs the 512 steps of the next), more tiles than CTAs, and scratch for the cost rows.
-    // Same results either way.
+    // costs with the decisions recomputed by the traceback chains (viterbi_lazy.cu), 0 = the
+    // latter where it pays: three or four bits or the dedicated K2 arithmetic (the generic K2
+    // arithmetic would have to store every 32 KiB cost row, which costs what the bookkeeping
+    // saves), full tail-biting context (a chain rides on the 256-step passes that follow), more
+    // tiles than CTAs, and scratch for the cost rows.  Same results either way.
     const int organisation = (variant >> 6) & 3;
     variant &= 1;
     if (organisation != 1) {
         const int sms = resident_ctas();
         if (sms <= 0) return qsrtb_fail(QSRTB_ECUDA, "cannot query the device");
-        const size_t per_cta = qsrtb_lazy_scratch_per_cta(bits);
+        const size_t per_cta = qsrtb_lazy_scratch_per_cta(bits, variant);
         int64_t grid = n_tiles < sms ? n_tiles : sms;
         // the state table is copied to shared memory and the cost rows are written 16 bytes at a time
         const bool aligned = (reinterpret_cast<uintptr_t>(lut_state) & 15) == 0 &&
@@ -420,7 +420,7 @@ int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const 
             return qsrtb_fail(QSRTB_ESCRATCH, "traceback scratch smaller than the cost rows of the grid, or table / scratch not 16-byte aligned");
         // with the chain riding on one warp, 512 threads with two units each (fewer warps per
         // scheduler, so the chain's warp falls less far behind) beat 1024 at every rate
-        if (fits && (organisation == 2 || (bits != 2 && context == 128 && n_tiles > sms)))
+        if (fits && (organisation == 2 || ((bits != 2 || variant == 1) && context == 128 && n_tiles > sms)))
             return qsrtb_lazy_launch(io, n_tiles, lut_state, lut_pm, bits, context, variant,
                                      layout != 0 ? layout : 2, scratch, int(grid), s);
     }

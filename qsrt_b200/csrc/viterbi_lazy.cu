@@ -40,6 +40,11 @@ constexpr int kInFlight = 3;      // tiles of a CTA whose input and states are l
 constexpr int kPrimerRows = 130;  // cost rows of a primer buffer (C + 1 used, C <= 128)
 
 enum ChainKind { CHAIN_CONSTRAINED = 0, CHAIN_PRIMER = 1 };
+// The warp that walks a chain.  With the dedicated K2 arithmetic warp 0 already folds the block
+// minimum every step, and the chains go to warps 2 and 3 (K2: 237 k against 228 k tiles/s); the
+// other arithmetics measured better with warps 0 and 1 (K3: 348 k against 337 k).
+template <int MODE>
+constexpr int chain_warp(int kind) { return (MODE == MODE_K2 ? 2 : 0) + kind; }
 
 // A traceback in flight.  `head` is what a link needs and changes with every link; the walking
 // warp reads and writes it with one 16-byte access.
@@ -74,8 +79,15 @@ struct LazySmem {
     int edge;
     int pad;
     TileSlot slot[kInFlight];
-    __align__(16) Chain chain[2];  // [CHAIN_CONSTRAINED] walked by warp 0, [CHAIN_PRIMER] by warp 1
+    __half shift_hist[2][kInFlight][256];  // dedicated K2: the shift each recorded step subtracted
+    __align__(16) Chain chain[2];  // [CHAIN_CONSTRAINED], [CHAIN_PRIMER]: each walked by its own warp
 };
+
+// The dedicated K2 arithmetic keeps every second cost row only (a K2 row is 32 KiB, and storing
+// all of them costs more than the bookkeeping they replace): a link that needs a missing row
+// recomputes the four costs it wants from the row before.
+template <int MODE>
+constexpr bool half_rows() { return MODE == MODE_K2; }
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src)
 {
@@ -162,17 +174,111 @@ __device__ __forceinline__ bool chain_link(Chain* ch, LazySmem* sm, const uint8_
     return true;
 }
 
+// ---- dedicated K2: every second cost row ------------------------------------------------------
+// Cost row q of a pass lives at rows + (q >> 1) rows, for even q only.  Lane 4k + j of the chain's
+// warp serves predecessor k of the link's out-edge and, where row q is missing, predecessor j of
+// that predecessor.
+__device__ __forceinline__ void chain_issue_half(Chain* ch, int q, int e, int lane)
+{
+    using G = Geo<2>;
+    const int k = (lane >> 2) & 3, j = lane & 3;
+    const int s_k = (e >> 2) + k * G::pred_stride;
+    if (lane < 16 && q >= 0) {
+        if (q & 1) {
+            const int pp = (s_k >> 2) + j * G::pred_stride;
+            cp_async4(&ch->cost_word[lane], ch->rows + (size_t(q >> 1) * G::edges + (pp & ~1)) * 2);
+        } else if (j == 0) {
+            cp_async4(&ch->cost_word[lane], ch->rows + (size_t(q >> 1) * G::edges + (s_k & ~1)) * 2);
+        }
+    }
+    cp_async_commit();
+}
+
+template <int KIND>
+__device__ __forceinline__ bool chain_link_half(Chain* ch, LazySmem* sm, const uint8_t* labels, int lane)
+{
+    using G = Geo<2>;
+    cp_async_wait_all();
+    const int4 h = *reinterpret_cast<const int4*>(&ch->head);
+    const int k = (lane >> 2) & 3, j = lane & 3;
+    const int ri = h.x, e = h.y & (G::edges - 1), slot = h.z;
+    const int s_k = (e >> 2) + k * G::pred_stride;
+    const uint32_t outer_label = labels[(k << G::Kr) | e];
+    const uint32_t inner_label = labels[(j << G::Kr) | s_k];
+    const uint32_t cw = ch->cost_word[lane & 15];
+    const int pre_state = ch->pre_state;
+    const int row_bias = ch->row_bias;
+    if (ri < 0) return false;
+    const int q = ri + row_bias;  // the cost row this link needs
+    __half p = __ushort_as_half(0);
+    if (q >= 0) {
+        if (q & 1) {
+            // costs after step q of the four predecessors, from the row before: the forward
+            // pass's own metric, minimum and shift (acs_step, MODE_K2)
+            const int symbol = KIND == CHAIN_CONSTRAINED ? q : q - 1;
+            const __half dh = __hsub(e4m3_to_half(inner_label), sm->in_h[slot][symbol & 255]);
+            const int pp = (s_k >> 2) + j * G::pred_stride;
+            const uint32_t bits = (pp & 1) ? (cw >> 16) : (cw & 0xffffu);
+            __half m = __hfma(dh, dh, __ushort_as_half(static_cast<unsigned short>(bits)));
+            m = __hmin(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = __hmin(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            p = __hsub(m, sm->shift_hist[KIND][slot][q & 255]);
+        } else {
+            const uint32_t bits = (s_k & 1) ? (cw >> 16) : (cw & 0xffffu);
+            p = __ushort_as_half(static_cast<unsigned short>(bits));
+        }
+    }
+    uint32_t key = 0xffffffffu;
+    if (lane < 16 && j == 0) {
+        const __half dh = __hsub(e4m3_to_half(outer_label), __ushort_as_half(static_cast<unsigned short>(h.w)));
+        __half v;
+        if (KIND == CHAIN_CONSTRAINED && ri == 0) {
+            v = __hmul(dh, dh);
+            if (s_k != pre_state) v = __ushort_as_half(0x7c00);
+        } else {
+            v = __hfma(dh, dh, p);
+        }
+        key = (half_key(__half_as_ushort(v)) << 5) | uint32_t(k);
+    }
+    key = __reduce_min_sync(0xffffffffu, key);
+    const int decision = int(key & 31u);
+    const int prev = (decision << (16 - 2 * 2)) | (e >> 2);
+    const int next = ri - 1;
+    if (next >= 0) chain_issue_half(ch, next + row_bias, prev, lane);
+    if (lane == 0) {
+        if constexpr (KIND == CHAIN_CONSTRAINED) sm->states[slot][ri] = uint16_t((prev << 2) | e);
+        const int w_bits = next >= 0 ? int(__half_as_ushort(sm->in_h[slot][next])) : 0;
+        *reinterpret_cast<int4*>(&ch->head) = make_int4(next, prev, slot, w_bits);
+        if (next < 0) {
+            ch->result = prev;
+            ch->state = 2;
+        }
+    }
+    __syncwarp();
+    return true;
+}
+
+// One link of a chain, whichever row layout its pass has.
+template <int K, int MODE, int KIND>
+__device__ __forceinline__ bool chain_step(Chain* ch, LazySmem* sm, const uint8_t* labels, int lane)
+{
+    if constexpr (half_rows<MODE>())
+        return chain_link_half<KIND>(ch, sm, labels, lane);
+    else
+        return chain_link<K, MODE, KIND>(ch, sm, labels, lane);
+}
+
 // Walk what is left of a chain without anything to hide the latency behind (normally nothing
 // is left).  The chain's warp only.
 template <int K, int MODE, int KIND>
 __device__ __forceinline__ void chain_drain(Chain* ch, LazySmem* sm, const uint8_t* labels, int lane)
 {
     for (int guard = 0; guard < 257; ++guard)
-        if (!chain_link<K, MODE, KIND>(ch, sm, labels, lane)) break;
+        if (!chain_step<K, MODE, KIND>(ch, sm, labels, lane)) break;
 }
 
 // Start a chain at (ri, edge) of the tile in `slot`.  All lanes of the chain's warp.
-template <int K>
+template <int K, int MODE>
 __device__ __forceinline__ void chain_start(Chain* ch, LazySmem* sm, const uint8_t* rows, int row_bias,
                                             int ri, int edge, int slot, int pre_state, long long tile,
                                             int lane)
@@ -188,7 +294,10 @@ __device__ __forceinline__ void chain_start(Chain* ch, LazySmem* sm, const uint8
             make_int4(ri, edge, slot, int(__half_as_ushort(sm->in_h[slot][ri])));
     }
     __syncwarp();
-    chain_issue<K>(ch, ri + row_bias, edge, lane);
+    if constexpr (half_rows<MODE>())
+        chain_issue_half(ch, ri + row_bias, edge, lane);
+    else
+        chain_issue<K>(ch, ri + row_bias, edge, lane);
 }
 
 // Where thread t (< 256) finds its value of `tile` and where the results go (see TileIO).
@@ -282,7 +391,7 @@ __device__ __forceinline__ void finish_constrained_chain(LazyCtx& cx)
     Chain* ch = &cx.sm->chain[CHAIN_CONSTRAINED];
     __syncthreads();
     if (ch->state == 0) return;
-    if ((threadIdx.x >> 5) == CHAIN_CONSTRAINED)
+    if ((threadIdx.x >> 5) == chain_warp<CHAIN_MODE>(CHAIN_CONSTRAINED))
         chain_drain<K, CHAIN_MODE, CHAIN_CONSTRAINED>(ch, cx.sm, cx.labels, threadIdx.x & 31);
     __syncthreads();
     store_tile(*cx.io, ch->tile, cx.sm->states[ch->head.slot], cx.lut_state);
@@ -298,7 +407,7 @@ __device__ __forceinline__ void finish_primer_chain(LazyCtx& cx)
     Chain* ch = &cx.sm->chain[CHAIN_PRIMER];
     __syncthreads();
     if (ch->state == 0) return;
-    if ((threadIdx.x >> 5) == CHAIN_PRIMER)
+    if ((threadIdx.x >> 5) == chain_warp<CHAIN_MODE>(CHAIN_PRIMER))
         chain_drain<K, CHAIN_MODE, CHAIN_PRIMER>(ch, cx.sm, cx.labels, threadIdx.x & 31);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -369,11 +478,11 @@ __device__ __forceinline__ bool run_pass(const uint32_t (&L)[UNITS][NL], LazyCtx
         if constexpr (decltype(chain_tag)::value) {
             if (cx.tick == cx.chain_due) {  // kNever in every warp but the two that walk chains
                 bool more;
-                if (warp == CHAIN_CONSTRAINED)
-                    more = chain_link<K, CHAIN_MODE, CHAIN_CONSTRAINED>(&sm->chain[CHAIN_CONSTRAINED], sm,
+                if (warp == chain_warp<CHAIN_MODE>(CHAIN_CONSTRAINED))
+                    more = chain_step<K, CHAIN_MODE, CHAIN_CONSTRAINED>(&sm->chain[CHAIN_CONSTRAINED], sm,
                                                                         cx.labels, lane);
                 else
-                    more = chain_link<K, CHAIN_MODE, CHAIN_PRIMER>(&sm->chain[CHAIN_PRIMER], sm, cx.labels,
+                    more = chain_step<K, CHAIN_MODE, CHAIN_PRIMER>(&sm->chain[CHAIN_PRIMER], sm, cx.labels,
                                                                    lane);
                 cx.chain_due = more ? cx.tick + kChainCadence : kNever;
             }
@@ -382,12 +491,19 @@ __device__ __forceinline__ bool run_pass(const uint32_t (&L)[UNITS][NL], LazyCtx
         const __half w = sm->in_h[slot][ri];
         // a recorded step's row: by symbol for decisions and constrained costs, by step for a
         // primer's costs (which start one step before the first recorded decision)
-        uint8_t* row = rows + size_t(COSTS && !CONSTRAINED ? i - first_row_step : ri) * row_stride;
+        const int row_index = COSTS && !CONSTRAINED ? i - first_row_step : ri;
+        constexpr bool HALF = COSTS && half_rows<MODE>();
+        uint8_t* row = rows + size_t(HALF ? row_index >> 1 : row_index) * row_stride;
         __half2 shift2 = u2h2(0u);
         __half2 step_min2 = u2h2(kInf2);
         if constexpr (MODE == MODE_K2) {
             if (i > 0) k2_fold(i);
             shift2 = __half2half2(sm->shift[i & 1]);
+            if constexpr (HALF) {
+                if (threadIdx.x == 0 && row_index >= 0)
+                    sm->shift_hist[CONSTRAINED ? CHAIN_CONSTRAINED : CHAIN_PRIMER][slot][row_index & 255] =
+                        sm->shift[i & 1];
+            }
         }
         if (i == 0) {
             if constexpr (MODE == MODE_K2)
@@ -403,7 +519,10 @@ __device__ __forceinline__ bool run_pass(const uint32_t (&L)[UNITS][NL], LazyCtx
                 ACS(MODE, false, false, false, track_max);
         } else {
             if constexpr (MODE == MODE_K2) {
-                ACS(MODE, false, false, true, step_min2);
+                if (HALF && (row_index & 1))  // the row between two stored ones
+                    ACS(MODE, false, false, false, step_min2);
+                else
+                    ACS(MODE, false, false, true, step_min2);
             } else if constexpr (MODE == MODE_FAST && CONSTRAINED) {
                 if (i < kSafeSteps)  // unreachable states exist for the first few constrained steps
                     ACS(MODE_SAFE, false, false, true, track_max);
@@ -458,10 +577,17 @@ __device__ __forceinline__ bool encode_with_decisions(const uint32_t (&L)[UNITS]
     return true;
 }
 
-template <int K>
+// Cost rows per CTA: two constrained and two primer buffers (half of the rows with the dedicated
+// K2 arithmetic, which stores every second one).
+template <bool DEDICATED>
+constexpr int constrained_buffer_rows() { return DEDICATED ? 128 : 256; }
+template <bool DEDICATED>
+constexpr int primer_buffer_rows() { return DEDICATED ? kPrimerRows / 2 : kPrimerRows; }
+template <int K, bool DEDICATED>
 constexpr size_t lazy_cta_bytes()
 {
-    return size_t(2 * 256 + 2 * kPrimerRows) * Geo<K>::edges * 2;  // two constrained and two primer buffers
+    return size_t(2 * constrained_buffer_rows<DEDICATED>() + 2 * primer_buffer_rows<DEDICATED>()) *
+           Geo<K>::edges * 2;
 }
 
 template <int K, bool DEDICATED, int UNITS>
@@ -484,10 +610,15 @@ viterbi_lazy_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
     for (int i = threadIdx.x; i < 65536 / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(labels)[i] = reinterpret_cast<const uint4*>(lut_state)[i];
     cx.labels = labels;
-    cx.scratch = scratch_base + size_t(blockIdx.x) * lazy_cta_bytes<K>();
+    cx.scratch = scratch_base + size_t(blockIdx.x) * lazy_cta_bytes<K, DEDICATED>();
     // buffers alternate between consecutive tiles
-    auto constrained_rows = [&](int x) { return cx.scratch + size_t((x & 1) * 256) * (G::edges * 2); };
-    auto primer_rows = [&](int x) { return cx.scratch + size_t(512 + (x & 1) * kPrimerRows) * (G::edges * 2); };
+    auto constrained_rows = [&](int x) {
+        return cx.scratch + size_t((x & 1) * constrained_buffer_rows<DEDICATED>()) * (G::edges * 2);
+    };
+    auto primer_rows = [&](int x) {
+        return cx.scratch + size_t(2 * constrained_buffer_rows<DEDICATED>() +
+                                   (x & 1) * primer_buffer_rows<DEDICATED>()) * (G::edges * 2);
+    };
     cx.lut_state = lut_state;
     cx.io = &io;
     cx.context = context;
@@ -567,11 +698,11 @@ viterbi_lazy_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
             boundary = boundary_argmin<K, K != 2, UNITS>(inc, sm->red);  // step before the last (cuh:375,401)
         if (lazy_primers) {
             finish_primer_chain<K, MODE>(cx);  // tile x - 1's: it had a constrained pass and this primer
-            if (warp == CHAIN_PRIMER)
-                chain_start<K>(&sm->chain[CHAIN_PRIMER], sm, rows, 0, context - 1, boundary, slot, -1,
+            if (warp == chain_warp<MODE>(CHAIN_PRIMER))
+                chain_start<K, MODE>(&sm->chain[CHAIN_PRIMER], sm, rows, 0, context - 1, boundary, slot, -1,
                                tile_of(x), lane);
-            cx.chain_due = warp == CHAIN_PRIMER ? cx.tick + kChainCadence
-                           : warp == CHAIN_CONSTRAINED ? cx.chain_due : kNever;
+            cx.chain_due = warp == chain_warp<MODE>(CHAIN_PRIMER) ? cx.tick + kChainCadence
+                           : warp == chain_warp<MODE>(CHAIN_CONSTRAINED) ? cx.chain_due : kNever;
             __syncthreads();
         } else {
             const int end_state = traceback<K, UNITS>(rows, reinterpret_cast<uint8_t*>(cx.cost0), context - 1,
@@ -603,11 +734,11 @@ viterbi_lazy_kernel(const TileIO io, const uint8_t* __restrict__ lut_pm,
             if (run_pass<K, MODE, UNITS, NL, true, true>(L, cx, slot, 0, 256, end_state, 0, rows, 0, cur, inc))
                 return x;
             finish_constrained_chain<K, MODE>(cx);  // tile x - 1's: it had a primer and this pass
-            if (warp == CHAIN_CONSTRAINED)
-                chain_start<K>(&sm->chain[CHAIN_CONSTRAINED], sm, rows, -1, 255, end_state, slot, end_state,
+            if (warp == chain_warp<MODE>(CHAIN_CONSTRAINED))
+                chain_start<K, MODE>(&sm->chain[CHAIN_CONSTRAINED], sm, rows, -1, 255, end_state, slot, end_state,
                                tile_of(x), lane);
-            cx.chain_due = warp == CHAIN_CONSTRAINED ? cx.tick + kChainCadence
-                           : warp == CHAIN_PRIMER ? cx.chain_due : kNever;
+            cx.chain_due = warp == chain_warp<MODE>(CHAIN_CONSTRAINED) ? cx.tick + kChainCadence
+                           : warp == chain_warp<MODE>(CHAIN_PRIMER) ? cx.chain_due : kNever;
             __syncthreads();
         } else {
             if (run_pass<K, MODE, UNITS, NL, true, false>(L, cx, slot, 0, 256, end_state, 0, rows, 0, cur, inc))
@@ -660,10 +791,11 @@ int launch_lazy(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, con
 
 }  // namespace
 
-size_t qsrtb_lazy_scratch_per_cta(int bits)
+size_t qsrtb_lazy_scratch_per_cta(int bits, int dedicated)
 {
-    // two constrained buffers of 256 cost rows and two primer buffers, rows of 2^(16-bits) halves
-    return size_t(2 * 256 + 2 * kPrimerRows) * (size_t(2) << (16 - bits));
+    // two constrained and two primer buffers of cost rows, rows of 2^(16-bits) halves
+    const size_t rows = (bits == 2 && dedicated) ? 2 * 128 + 2 * (kPrimerRows / 2) : 2 * 256 + 2 * kPrimerRows;
+    return rows * (size_t(2) << (16 - bits));
 }
 
 int qsrtb_lazy_launch(const qsrtb_vit::TileIO& io, int64_t n_tiles, const uint8_t* lut_state,
