@@ -68,17 +68,13 @@ __device__ __forceinline__ bool encode_tile(const uint32_t (&L)[UNITS][NL], Smem
     // the shift used by step s is the block minimum stored by step s-2 when that is >= 1024.
     auto k2_fold = [&](int s) {
         if (warp == 0) {
-            __half m = lane < WARPS ? sm->warp_mins[(s - 1) & 1][lane] : __ushort_as_half(0x7c00);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = __hmin(m, __shfl_down_sync(0xffffffffu, m, o));
+            const __half m = warp_min_half(lane < WARPS ? sm->warp_mins[(s - 1) & 1][lane] : __ushort_as_half(0x7c00));
             if (lane == 0)
                 sm->shift[(s + 1) & 1] = __hge(m, __float2half_rn(1024.0f)) ? m : __ushort_as_half(0);
         }
     };
     auto k2_publish = [&](int s, __half2 step_min2) {
-        __half m = __hmin(__low2half(step_min2), __high2half(step_min2));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = __hmin(m, __shfl_down_sync(0xffffffffu, m, o));
+        const __half m = warp_min_half(__hmin(__low2half(step_min2), __high2half(step_min2)));
         if (lane == 0) sm->warp_mins[s & 1][warp] = m;
     };
 

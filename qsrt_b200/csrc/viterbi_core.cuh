@@ -253,6 +253,14 @@ __device__ __forceinline__ uint32_t half_key(uint32_t h)
     return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
 }
 
+// Minimum of a half over the warp (no NaN among the inputs): one integer reduction on the
+// sortable keys instead of five dependent shuffle rounds.
+__device__ __forceinline__ __half warp_min_half(__half v)
+{
+    const uint32_t key = __reduce_min_sync(0xffffffffu, half_key(__half_as_ushort(v)));
+    return __ushort_as_half(static_cast<unsigned short>((key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu)));
+}
+
 // Boundary argmin with the reference's tie order.
 //   TREE512: the generic kernel for K != 2 reduces with 512 threads holding two interleaved
 //   streams (cuh:388-423); otherwise 1024 threads hold one stream (cuh:365-387, k2 cuh:276-325).
