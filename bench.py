@@ -702,17 +702,17 @@ def cpu_baseline(payload, bits: int) -> dict:
 # The search kernel a layer-sized launch gets at each rate, and its DRAM bytes per tile from the
 # ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
 SEARCH_KERNEL = {
-    2: "viterbi_kernel<2, dedicated, 2 units/thread> (survivor decisions)",
+    2: "viterbi_lazy_kernel<2, dedicated, 2 units/thread> (every second path-cost row, decisions recomputed by the traceback chains)",
     3: "viterbi_lazy_kernel<3, generic, 2 units/thread> (path costs, decisions recomputed by the traceback chains)",
     4: "viterbi_lazy_kernel<4, generic, 2 units/thread> (path costs, decisions recomputed by the traceback chains)",
 }
 NCU_DRAM_BYTES_PER_TILE = {
-    2: (823.1e6 + 337.3e6) / 592,
+    2: (6545.6e6 + 496.9e6) / 1184,
     3: (6528.9e6 + 500.5e6) / 1184,
     4: None,
 }
 NCU_DRAM_SOURCE = {
-    2: "ncu capture of a 592-tile launch, scaled per tile",
+    2: "ncu capture of a 1184-tile launch (8 tiles per CTA), scaled per tile",
     3: "ncu capture of a 1184-tile launch (8 tiles per CTA), scaled per tile",
     4: "not captured (half of the three-bit figure by construction: rows of 4096 states)",
 }
