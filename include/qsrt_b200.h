@@ -69,7 +69,8 @@ int qsrtb_viterbi_cost_scratch_bytes(int bits, int64_t n_tiles, size_t* bytes);
 /* `variant` of the search entry points: bit 0 = dedicated K2 arithmetic (bits == 2 only);
  * bits 4-5 = thread layout of the search kernel, a per-call tuning choice without a reference
  * counterpart (0 = the faster one for the rate and traceback organisation, 1 = 1024 threads
- * holding fp8 labels, 2 = 512 threads holding half2 labels in registers); bits 6-7 = what the search keeps for its traceback, also
+ * holding fp8 labels, 2 = 512 threads holding half2 labels in registers; the path-cost
+ * organisation below always runs 2); bits 6-7 = what the search keeps for its traceback, also
  * without a reference counterpart (1 = survivor decisions for every recorded step; 2 = path
  * costs, from which the tracebacks recompute the one decision per step they need while the
  * passes of the CTA's next tiles run - all passes but the constrained ones of a CTA's last two

@@ -414,11 +414,9 @@ int dispatch(const TileIO& io, int64_t n_tiles, const uint8_t* lut_state, const 
         const bool fits = aligned && scratch_bytes / per_cta >= size_t(grid);
         if (organisation == 2 && !fits)
             return qsrtb_fail(QSRTB_ESCRATCH, "traceback scratch smaller than the cost rows of the grid, or table / scratch not 16-byte aligned");
-        // with the chain riding on one warp, 512 threads with two units each (fewer warps per
-        // scheduler, so the chain's warp falls less far behind) beat 1024 at every rate
+        // (the thread layout bits do not apply: that kernel always runs 512 threads)
         if (fits && (organisation == 2 || ((bits != 2 || variant == 1) && context == 128 && n_tiles > sms)))
-            return qsrtb_lazy_launch(io, n_tiles, lut_state, lut_pm, bits, context, variant,
-                                     layout != 0 ? layout : 2, scratch, int(grid), s);
+            return qsrtb_lazy_launch(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, int(grid), s);
     }
     if (units == 1)
         return dispatch_units<1>(io, n_tiles, lut_state, lut_pm, bits, context, variant, scratch, scratch_bytes, s);

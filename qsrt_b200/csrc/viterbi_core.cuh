@@ -385,5 +385,5 @@ __device__ __forceinline__ int tensor_core_rc(int t, int& col)
 // owning qsrtb_lazy_scratch_per_cta(bits, dedicated) bytes of `scratch`.
 size_t qsrtb_lazy_scratch_per_cta(int bits, int dedicated);
 int qsrtb_lazy_launch(const qsrtb_vit::TileIO& io, int64_t n_tiles, const uint8_t* lut_state,
-                      const uint8_t* lut_pm, int bits, int context, int dedicated, int units,
-                      void* scratch, int grid, cudaStream_t stream);
+                      const uint8_t* lut_pm, int bits, int context, int dedicated, void* scratch, int grid,
+                      cudaStream_t stream);

@@ -795,25 +795,14 @@ size_t qsrtb_lazy_scratch_per_cta(int bits, int dedicated)
 }
 
 int qsrtb_lazy_launch(const qsrtb_vit::TileIO& io, int64_t n_tiles, const uint8_t* lut_state,
-                      const uint8_t* lut_pm, int bits, int context, int dedicated, int units,
-                      void* scratch, int grid, cudaStream_t stream)
+                      const uint8_t* lut_pm, int bits, int context, int dedicated, void* scratch, int grid,
+                      cudaStream_t stream)
 {
-    if (bits == 3) {
-        if (units == 1)
-            return launch_lazy<3, false, 1>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-        return launch_lazy<3, false, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-    }
-    if (bits == 4) {
-        if (units == 1)
-            return launch_lazy<4, false, 1>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-        return launch_lazy<4, false, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-    }
-    if (dedicated) {
-        if (units == 1)
-            return launch_lazy<2, true, 1>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-        return launch_lazy<2, true, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
-    }
-    if (units == 1)
-        return launch_lazy<2, false, 1>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
+    // Always 512 threads with two units each: with 1024 threads the chains' warps (one of eight
+    // on their scheduler instead of one of four) fall behind and delay every step's barrier
+    // (K3: 304 k against 349 k tiles/s), and 64 registers do not hold the kernel without spills.
+    if (bits == 3) return launch_lazy<3, false, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
+    if (bits == 4) return launch_lazy<4, false, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
+    if (dedicated) return launch_lazy<2, true, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
     return launch_lazy<2, false, 2>(io, n_tiles, lut_state, lut_pm, context, scratch, grid, stream);
 }
