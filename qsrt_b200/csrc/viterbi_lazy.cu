@@ -12,11 +12,13 @@
 //   * a chain is latency-bound (about a microsecond per link from HBM), so it never runs on its
 //     own: one warp advances it by a link every second trellis step of whatever pass the CTA is
 //     running (cp.async of the predecessors' cost words into shared memory, consumed two steps
-//     later).  Warp 0 walks the constrained pass's chain (256 links, writes the states), warp 1
-//     the primer's (C links, yields the boundary state);
+//     later).  One warp walks the constrained pass's chain (256 links, writes the states), the
+//     next one the primer's (C links, yields the boundary state);
 //   * a primer's boundary state is needed before the same tile's constrained pass can start, so
 //     a CTA interleaves its tiles: P(0) P(1) C(0) P(2) C(1) P(3) C(2) ...  The primer chain of
 //     tile x+1 is walked during C(x), the constrained chain of tile x during P(x+2) and C(x+1);
+//   * the dedicated K2 arithmetic, whose cost rows are 32 KiB, stores every second row only; a
+//     link that needs a missing row recomputes the four costs it wants from the row before;
 //   * the constrained passes of a CTA's last two tiles keep survivor decisions and the batched
 //     traceback of viterbi.cu (nothing follows them to hide a chain behind), as does every pass
 //     of a tile that met the fp16 clamp and is re-encoded with the literal arithmetic.
